@@ -1,0 +1,47 @@
+"""Shared pytest setup: marker registration and import paths.
+
+The package directory `flashattention-cuda_b200/` is not an importable name, so (like the reference's
+own conftest, tests/conftest.py:15-17, which puts its repo root on sys.path) it is added to
+sys.path here; `import fa_kernels` then resolves to the B200 implementation of that API.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+import pytest
+
+REPO_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG_DIR = os.path.join(REPO_ROOT, "flashattention-cuda_b200")
+GOLDEN_DIR = os.path.join(REPO_ROOT, "tests", "golden")
+for p in (PKG_DIR, REPO_ROOT):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+def pytest_collection_modifyitems(config, items):
+    try:
+        import torch
+        has_cuda = torch.cuda.is_available()
+    except Exception:
+        has_cuda = False
+    if has_cuda:
+        return
+    skip = pytest.mark.skip(reason="needs a CUDA GPU")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import numpy as np
+
+    def load(name):
+        return np.load(os.path.join(GOLDEN_DIR, name))
+    return load
