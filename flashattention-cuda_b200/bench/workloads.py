@@ -1,0 +1,42 @@
+"""Seeded synthetic inputs with the shapes, sizes and value distributions of the benchmark
+configurations.  Everything is generated on the device; the KV of a paged workload is drawn directly
+into the pool (for i.i.d. values that equals scattering a dense draw) and the block table is a random
+permutation of the physical pages."""
+
+from __future__ import annotations
+
+import torch
+
+
+def paged_gqa_decode(device, *, batch=64, h_q=32, h_kv=8, d=128, page_size=16, min_len=1024, max_len=8192,
+                     seed=2, kv_dtype=torch.float16, seq_lens=None):
+    """Paged GQA decode: one query token per sequence, context lengths uniform in [min_len, max_len],
+    block table = random permutation of the physical pages, K/V ~ N(0,1).
+
+    Returns a dict with q, k_pool, v_pool, block_table, page_size, seq_lens (python list) and the
+    algorithmic byte counts.
+    """
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    if seq_lens is None:
+        seq_lens = torch.randint(min_len, max_len + 1, (batch,), generator=g).tolist()
+    batch = len(seq_lens)
+    n_pages = [(n + page_size - 1) // page_size for n in seq_lens]
+    total_pages = sum(n_pages)
+    n_logical = max(n_pages)
+    perm = torch.randperm(total_pages, generator=g)
+    bt = torch.zeros(batch, n_logical, dtype=torch.int32)
+    cur = 0
+    for b, np_ in enumerate(n_pages):
+        bt[b, :np_] = perm[cur:cur + np_].to(torch.int32)
+        cur += np_
+    gd = torch.Generator(device=device).manual_seed(seed)
+    k_pool = torch.randn(total_pages, page_size, h_kv, d, device=device, dtype=torch.float32, generator=gd).to(kv_dtype)
+    v_pool = torch.randn(total_pages, page_size, h_kv, d, device=device, dtype=torch.float32, generator=gd).to(kv_dtype)
+    q = torch.randn(batch, h_q, 1, d, device=device, dtype=torch.float32, generator=gd).to(kv_dtype)
+    tokens = sum(seq_lens)
+    esz = k_pool.element_size()
+    kv_bytes = tokens * 2 * h_kv * d * esz
+    other = 2 * q.numel() * esz + 4 * total_pages
+    return dict(q=q, k_pool=k_pool, v_pool=v_pool, block_table=bt.to(device), block_table_host=bt,
+                page_size=page_size, seq_lens=seq_lens, tokens=tokens, kv_bytes=kv_bytes,
+                total_bytes=kv_bytes + other, flops=4 * h_q * d * tokens)

@@ -1,0 +1,810 @@
+// Paged GQA split-KV decode for sm_100a.
+//
+// One CTA (4 warps) serves one (sequence, KV head, key range, 16-row tile of packed query rows).
+// The G query heads that share a KV head are packed into the M dimension of the score product
+// (row m = i_q * G + g), so the KV bytes of a head are read once for the whole group.  Keys stream
+// through a multi-stage cp.async pipeline of 64-key tiles (16-byte coalesced loads of the page rows,
+// XOR-swizzled in shared memory so ldmatrix is conflict free); each warp owns 16 keys of a tile,
+// keeps its scores in registers (mma.sync m16n8k16, fp32 accumulate), runs an online softmax per
+// tile and accumulates P.V in registers.  FP8 E4M3 and NVFP4 pages are dequantised in registers
+// after ldmatrix (cvt.rn.f16x2.e4m3x2 / cvt.rn.f16x2.e2m1x2); the head-dim order of the contraction
+// is permuted per format so that no byte shuffling is needed on the K side.  The per-warp results
+// are combined in shared memory; the last CTA to finish a (sequence, head, row tile) merges the
+// partial results of all key ranges (arrival counter), so there is no second launch.
+//
+// Reference behaviour reproduced: kernels/v8_gqa_ss/gqa_ss_attention.cu:66-231 (M-packing
+// h_q = h_kv*G + g, block-table gather, q_offset causal mask, split + LSE merge),
+// kernels/v9_fp8/fp8_attention.cu:46-48,132-144 (E4M3 dequant x per-tensor scale),
+// kernels/v10_nvfp4/nvfp4_attention.cu:52-60,158-174 (E2M1 nibble x E4M3 micro-scale x tensor scale).
+
+#include <algorithm>
+#include <climits>
+#include <vector>
+
+#include "common.cuh"
+
+namespace fa {
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kTN = 16 * kWarps;     // keys per pipeline stage
+constexpr int kRowTile = 16;         // packed query rows per CTA
+constexpr int kMaxPages = 2048;      // block-table entries staged in shared memory per CTA
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+enum KvFmt { KV_F16 = 0, KV_BF16 = 1, KV_E4M3 = 2, KV_NVFP4 = 3 };
+
+struct DecodeParams {
+  const uint16_t* q;
+  const uint8_t* k_pool;
+  const uint8_t* v_pool;
+  const uint8_t* k_micro;
+  const uint8_t* v_micro;
+  const float* k_tok;
+  const float* v_tok;
+  const int32_t* block_table;
+  const int32_t* q_offsets;
+  const fa_decode_item* items;
+  void* out;
+  float* lse;
+  float* part_o;
+  float* part_lse;
+  int32_t* counters;
+  int32_t* status;
+  float k_scale, v_scale, softmax_scale;
+  int n_logical, num_blocks, page_size, page_shift;
+  int B, H_q, H_kv, N_q, G, M;
+  int causal, q_offset, out_dtype, bt_cap;
+};
+
+template <int D, int FMT>
+struct Geo {
+  static constexpr int KROW = (FMT == KV_NVFP4) ? D / 2 : (FMT == KV_E4M3 ? D : D * 2);  // bytes per key row
+  static constexpr int CPR = KROW / 16;                                                   // 16B chunks per row
+  static constexpr int MR = (FMT == KV_NVFP4) ? D / 16 : 0;                               // micro bytes per key
+  static constexpr int AUX = (FMT == KV_NVFP4) ? 2 * kTN * MR : (FMT == KV_E4M3 ? 2 * kTN * 4 : 0);
+  static constexpr int TILE = kTN * KROW;
+  static constexpr int STAGE = 2 * TILE + AUX;
+  static constexpr int MERGE = kWarps * kRowTile * (D + 2) * 4;
+};
+
+template <int KROW>
+__device__ __forceinline__ int swz(int row, int chunk) {
+  if constexpr (KROW >= 128) return chunk ^ (row & 7);
+  else if constexpr (KROW == 64) return chunk ^ ((row >> 1) & 3);
+  else return chunk ^ ((row >> 2) & 1);
+}
+
+// head-dim index of accumulator column e (0/1) of output tile t for lane-in-quad c
+template <int FMT>
+__device__ __forceinline__ int out_dim(int t, int c, int e) {
+  if constexpr (FMT == KV_E4M3) return 16 * (t >> 1) + 4 * c + 2 * e + (t & 1);
+  else if constexpr (FMT == KV_NVFP4) return 32 * (t >> 2) + 8 * c + 4 * e + (t & 3);
+  else return 8 * t + 2 * c + e;
+}
+// head-dim index of the first element of the A-fragment pair `sel` (0: a0/a1, 1: a2/a3) of k-step ks
+template <int FMT>
+__device__ __forceinline__ int q_dim(int ks, int c, int sel) {
+  if constexpr (FMT == KV_E4M3) return 16 * ks + 4 * c + 2 * sel;
+  else if constexpr (FMT == KV_NVFP4) return 32 * (ks >> 1) + 8 * c + 4 * (ks & 1) + 2 * sel;
+  else return 16 * ks + 2 * c + 8 * sel;
+}
+
+template <int D, int FMT, int NSTAGE, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const DecodeParams p) {
+  using G_ = Geo<D, FMT>;
+  constexpr int KROW = G_::KROW;
+  constexpr int CPR = G_::CPR;
+  constexpr int TILE = G_::TILE;
+  constexpr int STAGE = G_::STAGE;
+  constexpr int MR = G_::MR;
+  constexpr bool BF = (FMT == KV_BF16);
+  constexpr int NKS = D / 16;   // k-steps of the score product
+  constexpr int NOT = D / 8;    // 8-wide output tiles
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int PIPE_BYTES = (NSTAGE * STAGE > G_::MERGE) ? NSTAGE * STAGE : G_::MERGE;
+  int32_t* s_bt = reinterpret_cast<int32_t*>(smem + PIPE_BYTES);
+  __shared__ int s_ticket;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int g4 = lane >> 2, c = lane & 3;
+
+  const int item_idx = blockIdx.x / p.H_kv;
+  const int h_kv = blockIdx.x - item_idx * p.H_kv;
+  const int m0 = blockIdx.y * kRowTile;
+  const fa_decode_item it = p.items[item_idx];
+  const int b = it.b;
+  const int qoff = p.q_offsets ? p.q_offsets[b] : p.q_offset;
+
+  // ---- per-row limits (largest key index a row may attend) -------------------------------------
+  const int rows_valid = min(kRowTile, p.M - m0);
+  int lim[2];
+  int tile_max_lim = p.causal ? INT_MIN : INT_MAX, tile_min_lim = INT_MAX;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g4 + 8 * r;
+    lim[r] = INT_MAX;
+    if (p.causal && row < rows_valid) {
+      lim[r] = ((m0 + row) / p.G) + qoff;
+      tile_max_lim = max(tile_max_lim, lim[r]);
+      tile_min_lim = min(tile_min_lim, lim[r]);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    tile_max_lim = max(tile_max_lim, __shfl_xor_sync(0xffffffffu, tile_max_lim, o));
+    tile_min_lim = min(tile_min_lim, __shfl_xor_sync(0xffffffffu, tile_min_lim, o));
+  }
+  const int k_begin = it.k_begin;
+  int k_end = it.k_end;
+  if (p.causal) k_end = min(k_end, max(tile_max_lim, -1) + 1);
+  const int n_keys = max(k_end - k_begin, 0);
+  const int n_tiles = (n_keys + kTN - 1) / kTN;
+  const int mask_lim = min(tile_min_lim, k_end - 1);   // tiles reaching past this need masking
+  lim[0] = min(lim[0], k_end - 1);
+  lim[1] = min(lim[1], k_end - 1);
+
+  // ---- stage the block-table slice of this key range -------------------------------------------
+  const int pg0 = (p.page_shift >= 0) ? (k_begin >> p.page_shift) : (k_begin / p.page_size);
+  if (n_keys > 0) {
+    const int pg1 = (p.page_shift >= 0) ? ((k_end - 1) >> p.page_shift) : ((k_end - 1) / p.page_size);
+    const int32_t* bt = p.block_table + (int64_t)b * p.n_logical;
+    for (int i = tid; i <= pg1 - pg0 && i < p.bt_cap; i += kThreads) {
+      int pid = (pg0 + i < p.n_logical) ? bt[pg0 + i] : -2;
+      if ((unsigned)pid >= (unsigned)p.num_blocks) {   // never follow a bad table entry
+        if (p.status) atomicOr(p.status, 1);
+        pid = -1;
+      }
+      s_bt[i] = pid;
+    }
+  }
+
+  // ---- query fragments (registers, whole kernel) -----------------------------------------------
+  uint32_t qf[NKS][4];
+  {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g4 + 8 * r;
+      const int m = m0 + row;
+      const bool ok = row < rows_valid;
+      const int iq = ok ? m / p.G : 0;
+      const int g = ok ? m - iq * p.G : 0;
+      const uint16_t* qrow = p.q + (((int64_t)b * p.H_q + (h_kv * p.G + g)) * p.N_q + iq) * D;
+#pragma unroll
+      for (int ks = 0; ks < NKS; ++ks) {
+#pragma unroll
+        for (int sel = 0; sel < 2; ++sel) {
+          uint32_t v = 0;
+          if (ok) v = *reinterpret_cast<const uint32_t*>(qrow + q_dim<FMT>(ks, c, sel));
+          qf[ks][r + 2 * sel] = v;
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- producer: one 64-key tile of K and V (+ scales) into a stage ----------------------------
+  const int64_t row_stride_tok = (int64_t)p.H_kv;   // token rows are [page][tok][H_kv]
+  auto issue = [&](int stage, int kt) {
+    uint8_t* sk = smem + stage * STAGE;
+    uint8_t* sv = sk + TILE;
+    constexpr int RPP = kThreads / CPR;
+    constexpr int PASSES = (kTN + RPP - 1) / RPP;
+    const int chunk = tid % CPR;
+    const int r0 = tid / CPR;
+#pragma unroll
+    for (int i = 0; i < PASSES; ++i) {
+      const int r = r0 + i * RPP;
+      if (RPP > kTN && r >= kTN) break;
+      const int key = kt + r;
+      bool valid = key < k_end;
+      int64_t tokrow = 0;
+      if (valid) {
+        const int pg = (p.page_shift >= 0) ? (key >> p.page_shift) : (key / p.page_size);
+        const int pid = s_bt[pg - pg0];
+        const int off = key - pg * p.page_size;
+        valid = pid >= 0;
+        tokrow = ((int64_t)pid * p.page_size + off) * row_stride_tok + h_kv;
+      }
+      if (!valid) tokrow = 0;
+      const int sw = swz<KROW>(r, chunk) * 16;
+      cp_async16(smem_u32(sk + r * KROW + sw), p.k_pool + tokrow * KROW + chunk * 16, valid ? 16 : 0);
+      cp_async16(smem_u32(sv + r * KROW + sw), p.v_pool + tokrow * KROW + chunk * 16, valid ? 16 : 0);
+    }
+    if constexpr (FMT == KV_NVFP4 || FMT == KV_E4M3) {
+      if (FMT == KV_NVFP4 || p.k_tok != nullptr) {
+        // threads 0..63: K-side scale of key tid; threads 64..127: V-side scale of key tid-64
+        const int r = tid & (kTN - 1);
+        const bool is_v = tid >= kTN;
+        const int key = kt + r;
+        bool valid = key < k_end;
+        int64_t tokrow = 0;
+        if (valid) {
+          const int pg = (p.page_shift >= 0) ? (key >> p.page_shift) : (key / p.page_size);
+          const int pid = s_bt[pg - pg0];
+          const int off = key - pg * p.page_size;
+          valid = pid >= 0;
+          tokrow = ((int64_t)pid * p.page_size + off) * row_stride_tok + h_kv;
+        }
+        if (!valid) tokrow = 0;
+        uint8_t* aux = sv + TILE;
+        if constexpr (FMT == KV_NVFP4) {
+          const uint8_t* src = (is_v ? p.v_micro : p.k_micro) + tokrow * MR;
+          const uint32_t dst = smem_u32(aux + (is_v ? kTN * MR : 0) + r * MR);
+          if constexpr (MR == 8) cp_async8(dst, src, valid ? 8 : 0);
+          else cp_async4(dst, src, valid ? 4 : 0);
+        } else {
+          const float* src = (is_v ? p.v_tok : p.k_tok) + tokrow;
+          cp_async4(smem_u32(aux + (is_v ? kTN * 4 : 0) + r * 4), src, valid ? 4 : 0);
+        }
+      }
+    }
+  };
+
+  // ---- running state ----------------------------------------------------------------------------
+  float o[NOT][4];
+#pragma unroll
+  for (int t = 0; t < NOT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  const float sc_log2 = p.softmax_scale * kLog2e * p.k_scale;
+  const bool tok_scales = (FMT == KV_E4M3) && (p.k_tok != nullptr);
+
+#pragma unroll
+  for (int s = 0; s < NSTAGE - 1; ++s) {
+    if (s < n_tiles) issue(s, k_begin + s * kTN);
+    cp_async_commit();
+  }
+
+  for (int t = 0; t < n_tiles; ++t) {
+    cp_async_wait<NSTAGE - 2>();
+    __syncthreads();
+    {
+      const int nt = t + NSTAGE - 1;
+      if (nt < n_tiles) issue(nt % NSTAGE, k_begin + nt * kTN);
+      cp_async_commit();
+    }
+    const int stage = t % NSTAGE;
+    const uint8_t* sk = smem + stage * STAGE;
+    const uint8_t* sv = sk + TILE;
+    const uint8_t* aux = sv + TILE;
+    const int kt = k_begin + t * kTN;
+    const int kw = 16 * warp;   // this warp's first key within the tile
+
+    // ---------------- S = Q K^T for 16 keys -----------------------------------------------------
+    float s[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    {
+      const int krow = kw + (lane & 7) + ((lane >> 4) << 3);
+      const int csel = (lane >> 3) & 1;
+      const uint32_t kbase = smem_u32(sk + krow * KROW);
+      if constexpr (FMT == KV_F16 || FMT == KV_BF16) {
+#pragma unroll
+        for (int ks = 0; ks < NKS; ++ks) {
+          uint32_t r[4];
+          ldmatrix_x4(r, kbase + swz<KROW>(krow, 2 * ks + csel) * 16);
+          mma16816<BF>(s[0], qf[ks], r[0], r[1]);
+          mma16816<BF>(s[1], qf[ks], r[2], r[3]);
+        }
+      } else if constexpr (FMT == KV_E4M3) {
+#pragma unroll
+        for (int kp = 0; kp < NKS / 2; ++kp) {
+          uint32_t r[4];
+          ldmatrix_x4(r, kbase + swz<KROW>(krow, 2 * kp + csel) * 16);
+          mma16816<false>(s[0], qf[2 * kp], e4m3x2_to_h2(r[0]), e4m3x2_to_h2(r[0] >> 16));
+          mma16816<false>(s[0], qf[2 * kp + 1], e4m3x2_to_h2(r[1]), e4m3x2_to_h2(r[1] >> 16));
+          mma16816<false>(s[1], qf[2 * kp], e4m3x2_to_h2(r[2]), e4m3x2_to_h2(r[2] >> 16));
+          mma16816<false>(s[1], qf[2 * kp + 1], e4m3x2_to_h2(r[3]), e4m3x2_to_h2(r[3] >> 16));
+        }
+      } else {
+        // NVFP4: one 16-byte chunk = 32 head dims = 2 k-steps; lane-in-quad c owns dims 8c..8c+7 of
+        // the chunk, which lie inside micro block 2*chunk + (c >> 1).
+        const uint8_t* kmic = aux;
+        uint32_t mic[2];   // per n-tile: the D/32 micro bytes this lane needs, one per chunk
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const uint8_t* mrow = kmic + (kw + 8 * n + g4) * MR;
+          if constexpr (MR == 8) {
+            const uint2 w = *reinterpret_cast<const uint2*>(mrow);
+            mic[n] = prmt(w.x, w.y, (c >> 1) ? 0x7531u : 0x6420u);
+          } else {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(mrow);
+            mic[n] = prmt(w, 0u, (c >> 1) ? 0x4431u : 0x4420u);
+          }
+        }
+#pragma unroll
+        for (int kp = 0; kp < (D / 64 > 0 ? D / 64 : 1); ++kp) {
+          uint32_t r[4];
+          ldmatrix_x4(r, kbase + swz<KROW>(krow, 2 * kp + csel) * 16);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int n = j >> 1;              // r0,r1 -> keys 0-7 ; r2,r3 -> keys 8-15
+            const int ch = 2 * kp + (j & 1);   // chunk index
+            uint32_t h[4];
+            e2m1x8_to_h2x4(r[j], h);
+            const uint32_t mb = (mic[n] >> (8 * ch)) & 0xffu;
+            const uint32_t mh = e4m3x2_to_h2(mb | (mb << 8));
+            mma16816<false>(s[n], qf[2 * ch], hmul2_u32(h[0], mh), hmul2_u32(h[1], mh));
+            mma16816<false>(s[n], qf[2 * ch + 1], hmul2_u32(h[2], mh), hmul2_u32(h[3], mh));
+          }
+        }
+      }
+    }
+
+    // ---------------- scale, mask, online softmax ------------------------------------------------
+    float vsc[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
+    if constexpr (FMT == KV_E4M3) {
+      if (tok_scales) {
+        const float* ks_s = reinterpret_cast<const float*>(aux);
+        const float* vs_s = ks_s + kTN;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const float2 kk = *reinterpret_cast<const float2*>(ks_s + kw + 8 * n + 2 * c);
+          const float2 vv = *reinterpret_cast<const float2*>(vs_s + kw + 8 * n + 2 * c);
+          s[n][0] *= kk.x; s[n][1] *= kk.y; s[n][2] *= kk.x; s[n][3] *= kk.y;
+          vsc[n][0] = vv.x; vsc[n][1] = vv.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[n][e] *= sc_log2;
+    if (kt + kTN - 1 > mask_lim) {
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kt + kw + 8 * n + 2 * c + (e & 1);
+          if (key > lim[e >> 1]) s[n][e] = -INFINITY;
+        }
+    }
+    float alpha[2];
+    bool changed = false;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[r], mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[r] = fast_exp2(m_run[r] - m_use);
+      changed |= (m_new != m_run[r]);
+      m_run[r] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        s[n][2 * r] = fast_exp2(s[n][2 * r] - m_use);
+        s[n][2 * r + 1] = fast_exp2(s[n][2 * r + 1] - m_use);
+        sum += s[n][2 * r] + s[n][2 * r + 1];
+      }
+      l_run[r] = l_run[r] * alpha[r] + sum;
+    }
+    if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll
+      for (int tt = 0; tt < NOT; ++tt) {
+        o[tt][0] *= alpha[0]; o[tt][1] *= alpha[0];
+        o[tt][2] *= alpha[1]; o[tt][3] *= alpha[1];
+      }
+    }
+
+    // ---------------- O += P V --------------------------------------------------------------------
+    uint32_t pa[4];
+    if constexpr (BF) {
+      pa[0] = pack_bf2(s[0][0], s[0][1]); pa[1] = pack_bf2(s[0][2], s[0][3]);
+      pa[2] = pack_bf2(s[1][0], s[1][1]); pa[3] = pack_bf2(s[1][2], s[1][3]);
+    } else {
+      pa[0] = pack_h2(s[0][0] * vsc[0][0], s[0][1] * vsc[0][1]);
+      pa[1] = pack_h2(s[0][2] * vsc[0][0], s[0][3] * vsc[0][1]);
+      pa[2] = pack_h2(s[1][0] * vsc[1][0], s[1][1] * vsc[1][1]);
+      pa[3] = pack_h2(s[1][2] * vsc[1][0], s[1][3] * vsc[1][1]);
+    }
+    {
+      const int vrow = kw + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int csel = lane >> 4;
+      const uint32_t vbase = smem_u32(sv + vrow * KROW);
+      if constexpr (FMT == KV_F16 || FMT == KV_BF16) {
+#pragma unroll
+        for (int jp = 0; jp < D / 16; ++jp) {
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, vbase + swz<KROW>(vrow, 2 * jp + csel) * 16);
+          mma16816<BF>(o[2 * jp], pa, r[0], r[1]);
+          mma16816<BF>(o[2 * jp + 1], pa, r[2], r[3]);
+        }
+      } else if constexpr (FMT == KV_E4M3) {
+        // after the 16-bit transpose a register holds (k0,d0)(k0,d1)(k1,d0)(k1,d1); regroup to
+        // (k0,d0)(k1,d0) | (k0,d1)(k1,d1): even head dims feed tile 2j, odd head dims tile 2j+1.
+#pragma unroll
+        for (int jp = 0; jp < D / 32; ++jp) {
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, vbase + swz<KROW>(vrow, 2 * jp + csel) * 16);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const uint32_t x0 = prmt(r[2 * u], 0u, 0x3120u);
+            const uint32_t x1 = prmt(r[2 * u + 1], 0u, 0x3120u);
+            const int j = 2 * jp + u;
+            mma16816<false>(o[2 * j], pa, e4m3x2_to_h2(x0), e4m3x2_to_h2(x1));
+            mma16816<false>(o[2 * j + 1], pa, e4m3x2_to_h2(x0 >> 16), e4m3x2_to_h2(x1 >> 16));
+          }
+        }
+      } else {
+        // NVFP4 V: a 16-bit unit holds 4 head dims of one key.  Lane g4 owns unit g4 of the chunk
+        // (dims 4*g4..4*g4+3, micro block 2*chunk + (g4 >> 2)) for keys 2c, 2c+1 (and +8).
+        const uint8_t* vmic = aux + kTN * MR;
+        uint32_t mlo[2], mhi[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint8_t* r0p = vmic + (kw + 8 * u + 2 * c) * MR;
+          uint32_t a, bq;
+          if constexpr (MR == 8) {
+            const uint2 w0 = *reinterpret_cast<const uint2*>(r0p);
+            const uint2 w1 = *reinterpret_cast<const uint2*>(r0p + MR);
+            const uint32_t sel = (g4 >> 2) ? 0x7531u : 0x6420u;
+            a = prmt(w0.x, w0.y, sel);
+            bq = prmt(w1.x, w1.y, sel);
+          } else {
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(r0p);
+            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(r0p + MR);
+            const uint32_t sel = (g4 >> 2) ? 0x4431u : 0x4420u;
+            a = prmt(w0, 0u, sel);
+            bq = prmt(w1, 0u, sel);
+          }
+          // interleave: chunk ch -> bytes (a[ch], b[ch])
+          mlo[u] = prmt(a, bq, 0x5140u);   // chunks 0,1
+          mhi[u] = prmt(a, bq, 0x7362u);   // chunks 2,3
+        }
+#pragma unroll
+        for (int jp = 0; jp < (D / 64 > 0 ? D / 64 : 1); ++jp) {
+          uint32_t r[4];
+          ldmatrix_x4_trans(r, vbase + swz<KROW>(vrow, 2 * jp + csel) * 16);
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int ch = 2 * jp + cc;
+            uint32_t bfrag[2][4];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              uint32_t h[4];
+              e2m1x8_to_h2x4(r[2 * cc + u], h);
+              const uint32_t mw = (ch < 2) ? mlo[u] : mhi[u];
+              const uint32_t mm = e4m3x2_to_h2(mw >> (16 * (ch & 1)));
+              bfrag[u][0] = hmul2_u32(prmt(h[0], h[2], 0x5410u), mm);
+              bfrag[u][1] = hmul2_u32(prmt(h[0], h[2], 0x7632u), mm);
+              bfrag[u][2] = hmul2_u32(prmt(h[1], h[3], 0x5410u), mm);
+              bfrag[u][3] = hmul2_u32(prmt(h[1], h[3], 0x7632u), mm);
+            }
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) mma16816<false>(o[4 * ch + qd], pa, bfrag[0][qd], bfrag[1][qd]);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- combine the four warps ---------------------------------------------------------------------
+  cp_async_wait<0>();
+  __syncthreads();
+  float* s_o = reinterpret_cast<float*>(smem);                 // [warp][16][D]
+  float* s_m = s_o + kWarps * kRowTile * D;                    // [warp][16]
+  float* s_l = s_m + kWarps * kRowTile;                        // [warp][16]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  {
+    const float out_scale = p.v_scale;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g4 + 8 * r;
+      if (row < rows_valid) {
+        float* dst = s_o + (warp * kRowTile + row) * D;
+#pragma unroll
+        for (int t = 0; t < NOT; ++t) {
+          dst[out_dim<FMT>(t, c, 0)] = o[t][2 * r] * out_scale;
+          dst[out_dim<FMT>(t, c, 1)] = o[t][2 * r + 1] * out_scale;
+        }
+        if (c == 0) {
+          s_m[warp * kRowTile + row] = m_run[r];
+          s_l[warp * kRowTile + row] = l_run[r];
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  const bool single = (it.n_split == 1);
+  const int slot = it.slot_base + it.split;
+  for (int idx = tid; idx < rows_valid * D; idx += kThreads) {
+    const int row = idx / D, dd = idx - row * D;
+    float mw[kWarps];
+    float mstar = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      mw[w] = s_m[w * kRowTile + row];
+      mstar = fmaxf(mstar, mw[w]);
+    }
+    const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float wgt = fast_exp2(mw[w] - m_use);
+      acc += wgt * s_o[(w * kRowTile + row) * D + dd];
+      l += wgt * s_l[w * kRowTile + row];
+    }
+    const float val = (l > 0.f) ? acc / l : 0.f;
+    const float lse = (l > 0.f) ? (m_use + log2f(l)) * kLn2 : -INFINITY;
+    const int m = m0 + row;
+    const int iq = m / p.G, g = m - iq * p.G;
+    const int64_t orow = ((int64_t)b * p.H_q + (h_kv * p.G + g)) * p.N_q + iq;
+    if (single) {
+      store_out_dyn(p.out, p.out_dtype, orow * D + dd, val);
+      if (p.lse && dd == 0) p.lse[orow] = lse;
+    } else {
+      const int64_t prow = ((int64_t)slot * p.H_q + (h_kv * p.G + g)) * p.N_q + iq;
+      p.part_o[prow * D + dd] = val;
+      if (dd == 0) p.part_lse[prow] = lse;
+    }
+  }
+  if (single) return;
+
+  // ---- last CTA of this (sequence, head, row tile) merges all key ranges -------------------------
+  __threadfence();
+  __syncthreads();
+  const int cidx = (b * p.H_kv + h_kv) * gridDim.y + blockIdx.y;
+  if (tid == 0) s_ticket = atomicAdd(p.counters + cidx, 1);
+  __syncthreads();
+  if (s_ticket != it.n_split - 1) return;
+  __threadfence();
+  if (tid == 0) p.counters[cidx] = 0;   // self-reset for the next launch
+  for (int idx = tid; idx < rows_valid * D; idx += kThreads) {
+    const int row = idx / D, dd = idx - row * D;
+    const int m = m0 + row;
+    const int iq = m / p.G, g = m - iq * p.G;
+    const int64_t hrow = (int64_t)(h_kv * p.G + g) * p.N_q + iq;
+    const int64_t slot_stride = (int64_t)p.H_q * p.N_q;
+    float mstar = -INFINITY;
+    for (int sidx = 0; sidx < it.n_split; ++sidx)
+      mstar = fmaxf(mstar, __ldcg(p.part_lse + (it.slot_base + sidx) * slot_stride + hrow));
+    const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+    float acc = 0.f, l = 0.f;
+    for (int sidx = 0; sidx < it.n_split; ++sidx) {
+      const int64_t prow = (it.slot_base + sidx) * slot_stride + hrow;
+      const float wgt = __expf(__ldcg(p.part_lse + prow) - m_use);
+      acc += wgt * __ldcg(p.part_o + prow * D + dd);
+      l += wgt;
+    }
+    const int64_t orow = (int64_t)b * p.H_q * p.N_q + hrow;
+    store_out_dyn(p.out, p.out_dtype, orow * D + dd, (l > 0.f) ? acc / l : 0.f);
+    if (p.lse && dd == 0) p.lse[orow] = (l > 0.f) ? m_use + __logf(l) : -INFINITY;
+  }
+}
+
+template <int D, int FMT, int NSTAGE, int MINB>
+int launch_decode(const DecodeParams& p, int n_items, int row_tiles, cudaStream_t stream) {
+  using G_ = Geo<D, FMT>;
+  constexpr int PIPE = (NSTAGE * G_::STAGE > G_::MERGE) ? NSTAGE * G_::STAGE : G_::MERGE;
+  const int SMEM = PIPE + p.bt_cap * 4;
+  constexpr int SMEM_MAX = PIPE + kMaxPages * 4;
+  auto kern = paged_decode_kernel<D, FMT, NSTAGE, MINB>;
+  static int configured_device = -1;   // attribute is per device
+  int dev = 0;
+  FA_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    FA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX));
+    configured_device = dev;
+  }
+  dim3 grid((unsigned)(n_items * p.H_kv), (unsigned)row_tiles);
+  kern<<<grid, kThreads, SMEM, stream>>>(p);
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
+}
+
+}  // namespace
+
+// ---- merge of rank-major partials --------------------------------------------------------------
+__global__ void merge_partials_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
+                                      int n_parts, int64_t rows, int D, void* out, int out_dtype,
+                                      float* lse_out) {
+  const int64_t row = blockIdx.x;
+  float mstar = -INFINITY;
+  for (int s = 0; s < n_parts; ++s) mstar = fmaxf(mstar, lse_parts[s * rows + row]);
+  const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+  float l = 0.f;
+  for (int s = 0; s < n_parts; ++s) l += __expf(lse_parts[s * rows + row] - m_use);
+  for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_parts; ++s)
+      acc += __expf(lse_parts[s * rows + row] - m_use) * o_parts[(s * rows + row) * D + dd];
+    store_out_dyn(out, out_dtype, row * D + dd, (l > 0.f) ? acc / l : 0.f);
+  }
+  if (lse_out && threadIdx.x == 0) lse_out[row] = (l > 0.f) ? m_use + __logf(l) : -INFINITY;
+}
+
+}  // namespace fa
+
+using namespace fa;
+
+extern "C" int fa_decode_plan_max_items(const int32_t* seq_lens_host, int n_k, int B, int page_size) {
+  (void)page_size;
+  int64_t total = 0;
+  for (int b = 0; b < B; ++b) total += (seq_lens_host ? std::max(seq_lens_host[b], 0) : std::max(n_k, 0)) / kTN + 2;
+  return (int)std::min<int64_t>(total, INT_MAX);
+}
+
+extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int H_kv, int rows, int page_size,
+                              int num_sms, int chunk_hint, fa_decode_item* items, int max_items,
+                              int* n_items, int* max_range_keys) {
+  FA_CHECK_ARG(B >= 1 && H_kv >= 1 && rows >= 1 && page_size >= 1, "fa_decode_plan: B, H_kv, rows, page_size must be >= 1");
+  FA_CHECK_ARG(items && n_items && max_range_keys, "fa_decode_plan: null output pointer");
+  if (num_sms <= 0) num_sms = 148;
+  const int row_tiles = (rows + kRowTile - 1) / kRowTile;
+  int64_t total = 0;
+  for (int b = 0; b < B; ++b) {
+    const int len = seq_lens_host ? seq_lens_host[b] : n_k;
+    FA_CHECK_ARG(len >= 0, "fa_decode_plan: negative sequence length at b=%d", b);
+    total += len;
+  }
+  // ranges of ~equal size, enough of them for ~8 waves of 2 CTAs per SM, never shorter than 256 keys
+  const int64_t max_chunk = (int64_t)(kMaxPages - 1) * page_size / kTN * kTN;
+  FA_CHECK_ARG(max_chunk >= kTN, "fa_decode_plan: page_size too small");
+  int64_t chunk;
+  if (chunk_hint > 0) {
+    chunk = chunk_hint;
+  } else {
+    const int64_t target_ctas = (int64_t)num_sms * 2 * 8;
+    chunk = (total * H_kv * row_tiles + target_ctas - 1) / target_ctas;
+    chunk = std::max<int64_t>(chunk, 256);
+  }
+  chunk = (chunk + kTN - 1) / kTN * kTN;
+  chunk = std::min(chunk, max_chunk);
+
+  std::vector<fa_decode_item> v;
+  int slot = 0;
+  int max_range = 0;
+  for (int b = 0; b < B; ++b) {
+    const int len = seq_lens_host ? seq_lens_host[b] : n_k;
+    int ns = (int)std::max<int64_t>((len + chunk - 1) / chunk, 1);
+    int64_t cb = ((len + ns - 1) / ns + kTN - 1) / kTN * kTN;
+    if (cb <= 0) cb = kTN;
+    ns = (int)std::max<int64_t>((len + cb - 1) / cb, 1);
+    for (int s = 0; s < ns; ++s) {
+      fa_decode_item it{};
+      it.b = b;
+      it.k_begin = (int)std::min<int64_t>((int64_t)s * cb, len);
+      it.k_end = (int)std::min<int64_t>((int64_t)(s + 1) * cb, len);
+      it.slot_base = slot;
+      it.n_split = ns;
+      it.split = s;
+      max_range = std::max(max_range, it.k_end - it.k_begin);
+      v.push_back(it);
+    }
+    slot += ns;
+  }
+  std::stable_sort(v.begin(), v.end(), [](const fa_decode_item& a, const fa_decode_item& b2) {
+    return (a.k_end - a.k_begin) > (b2.k_end - b2.k_begin);
+  });
+  if ((int)v.size() > max_items) return fail(FA_ERR_INVALID, "fa_decode_plan: %zu items exceed capacity %d", v.size(), max_items);
+  std::copy(v.begin(), v.end(), items);
+  *n_items = (int)v.size();
+  *max_range_keys = max_range;
+  return FA_OK;
+}
+
+extern "C" size_t fa_decode_workspace_bytes(int n_slots, int H_q, int N_q, int D) {
+  return (size_t)n_slots * H_q * N_q * (D + 1) * 4;
+}
+
+extern "C" size_t fa_decode_counters_len(int B, int H_q, int H_kv, int N_q) {
+  const int G = H_kv > 0 ? H_q / H_kv : 1;
+  const int row_tiles = (G * N_q + kRowTile - 1) / kRowTile;
+  return (size_t)B * H_kv * row_tiles + 1;   // +1 status word
+}
+
+extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
+  FA_CHECK_ARG(a != nullptr, "fa_paged_decode_fwd: null args");
+  FA_CHECK_ARG(a->q && a->k_pool && a->v_pool && a->block_table && a->items && a->out,
+               "fa_paged_decode_fwd: q, k_pool, v_pool, block_table, items, out must be non-null");
+  FA_CHECK_ARG(a->B >= 1 && a->H_q >= 1 && a->H_kv >= 1 && a->N_q >= 1, "fa_paged_decode_fwd: bad B/H/N_q");
+  FA_CHECK_ARG(a->H_q % a->H_kv == 0,
+               "H_q must be a positive multiple of H_kv (GQA group factor G = H_q/H_kv); got H_q=%d H_kv=%d",
+               a->H_q, a->H_kv);
+  if (a->D != 64 && a->D != 128) return fail(FA_ERR_UNSUPPORTED, "paged decode supports head_dim 64 or 128 (got %d)", a->D);
+  FA_CHECK_ARG(a->page_size >= 1 && a->n_logical >= 1 && a->num_blocks >= 1, "bad page_size / n_logical / num_blocks");
+  FA_CHECK_ARG(a->n_items >= 1, "empty plan");
+  FA_CHECK_ARG(a->out_dtype == FA_F32 || a->out_dtype == FA_F16 || a->out_dtype == FA_BF16, "out_dtype must be f32/f16/bf16");
+  int fmt;
+  switch (a->kv_dtype) {
+    case FA_F16: fmt = KV_F16; FA_CHECK_ARG(a->q_dtype == FA_F16, "f16 pools need f16 q"); break;
+    case FA_BF16: fmt = KV_BF16; FA_CHECK_ARG(a->q_dtype == FA_BF16, "bf16 pools need bf16 q"); break;
+    case FA_E4M3: fmt = KV_E4M3; FA_CHECK_ARG(a->q_dtype == FA_F16, "e4m3 pools need f16 q"); break;
+    case FA_NVFP4:
+      fmt = KV_NVFP4;
+      FA_CHECK_ARG(a->q_dtype == FA_F16, "nvfp4 pools need f16 q");
+      FA_CHECK_ARG(a->k_micro && a->v_micro, "nvfp4 pools need micro-scale pools");
+      break;
+    default: return fail(FA_ERR_INVALID, "unknown kv_dtype %d", a->kv_dtype);
+  }
+  FA_CHECK_ARG((a->k_token_scale == nullptr) == (a->v_token_scale == nullptr), "k/v token scales must both be set or both null");
+  FA_CHECK_ARG(a->k_token_scale == nullptr || fmt == KV_E4M3, "per-token scales are only defined for e4m3 pools");
+
+  const int G = a->H_q / a->H_kv;
+  const int M = G * a->N_q;
+  const int row_tiles = (M + kRowTile - 1) / kRowTile;
+  FA_CHECK_ARG(row_tiles <= 65535, "too many query rows per KV head (%d)", M);
+
+  FA_CHECK_ARG(a->n_slots == 0 || a->n_slots == a->n_items, "n_slots must be 0 (no sequence is split) or n_items");
+  FA_CHECK_ARG(a->max_range_keys >= 0, "max_range_keys must be >= 0");
+  const size_t need = fa_decode_workspace_bytes(a->n_slots, a->H_q, a->N_q, a->D);
+  FA_CHECK_ARG(need == 0 || a->workspace != nullptr, "workspace must be non-null when a sequence is split");
+  if (a->workspace_bytes < need) return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, need);
+  const size_t n_counters = fa_decode_counters_len(a->B, a->H_q, a->H_kv, a->N_q);
+  FA_CHECK_ARG(a->counters != nullptr, "counters must be non-null");
+  if (a->counters_len < n_counters) return fail(FA_ERR_WORKSPACE, "counters hold %zu ints < %zu", a->counters_len, n_counters);
+
+  DecodeParams p{};
+  p.q = reinterpret_cast<const uint16_t*>(a->q);
+  p.k_pool = reinterpret_cast<const uint8_t*>(a->k_pool);
+  p.v_pool = reinterpret_cast<const uint8_t*>(a->v_pool);
+  p.k_micro = reinterpret_cast<const uint8_t*>(a->k_micro);
+  p.v_micro = reinterpret_cast<const uint8_t*>(a->v_micro);
+  p.k_tok = a->k_token_scale;
+  p.v_tok = a->v_token_scale;
+  p.block_table = a->block_table;
+  p.q_offsets = a->q_offsets;
+  p.items = a->items;
+  p.out = a->out;
+  p.lse = a->lse;
+  p.counters = a->counters;
+  p.status = p.counters + (n_counters - 1);
+  p.part_o = reinterpret_cast<float*>(a->workspace);
+  p.part_lse = p.part_o + (size_t)a->n_slots * a->H_q * a->N_q * a->D;
+  p.bt_cap = a->max_range_keys / a->page_size + 2;
+  if (p.bt_cap > kMaxPages) return fail(FA_ERR_INVALID, "key range of %d keys spans more than %d pages", a->max_range_keys, kMaxPages);
+  p.k_scale = a->k_scale;
+  p.v_scale = a->v_scale;
+  p.softmax_scale = a->softmax_scale;
+  p.n_logical = a->n_logical;
+  p.num_blocks = a->num_blocks;
+  p.page_size = a->page_size;
+  p.page_shift = ((a->page_size & (a->page_size - 1)) == 0) ? __builtin_ctz((unsigned)a->page_size) : -1;
+  p.B = a->B; p.H_q = a->H_q; p.H_kv = a->H_kv; p.N_q = a->N_q; p.G = G; p.M = M;
+  p.causal = a->causal; p.q_offset = a->q_offset; p.out_dtype = a->out_dtype;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+
+#define FA_LAUNCH(D_, F_, NS_, MB_) return launch_decode<D_, F_, NS_, MB_>(p, a->n_items, row_tiles, st)
+  if (a->D == 128) {
+    switch (fmt) {
+      case KV_F16: if (a->variant == 1) FA_LAUNCH(128, KV_F16, 4, 1); FA_LAUNCH(128, KV_F16, 3, 2);
+      case KV_BF16: FA_LAUNCH(128, KV_BF16, 3, 2);
+      case KV_E4M3: if (a->variant == 1) FA_LAUNCH(128, KV_E4M3, 6, 2); FA_LAUNCH(128, KV_E4M3, 4, 3);
+      default: if (a->variant == 1) FA_LAUNCH(128, KV_NVFP4, 8, 2); FA_LAUNCH(128, KV_NVFP4, 6, 3);
+    }
+  } else {
+    switch (fmt) {
+      case KV_F16: FA_LAUNCH(64, KV_F16, 4, 3);
+      case KV_BF16: FA_LAUNCH(64, KV_BF16, 4, 3);
+      case KV_E4M3: FA_LAUNCH(64, KV_E4M3, 4, 3);
+      default: FA_LAUNCH(64, KV_NVFP4, 6, 3);
+    }
+  }
+#undef FA_LAUNCH
+}
+
+extern "C" int fa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int64_t rows, int D,
+                                 void* out, int out_dtype, float* lse_out, void* stream) {
+  FA_CHECK_ARG(o_parts && lse_parts && out, "fa_merge_partials: null pointer");
+  FA_CHECK_ARG(n_parts >= 1 && rows >= 1 && D >= 1, "fa_merge_partials: bad sizes");
+  FA_CHECK_ARG(rows <= INT_MAX, "fa_merge_partials: too many rows");
+  FA_CHECK_ARG(out_dtype == FA_F32 || out_dtype == FA_F16 || out_dtype == FA_BF16, "out_dtype must be f32/f16/bf16");
+  const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : 64);
+  merge_partials_kernel<<<(unsigned)rows, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      o_parts, lse_parts, n_parts, rows, D, out, out_dtype, lse_out);
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
+}

@@ -1,0 +1,34 @@
+"""The `forward` of each operator family with the reference's positional signatures
+(kernels/*/binding.cpp) plus keyword-only extensions (`out_dtype`, `return_lse`, per-sequence
+lengths through `n_k`, per-token FP8 scales through tensor-valued `scale_k` / `scale_v`)."""
+
+from __future__ import annotations
+
+import torch
+
+from . import _decode
+
+
+def paged_forward(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal=False, q_offset=0, **kw):
+    """kernels/v7_paged/binding.cpp, kernels/v8_gqa_ss/binding.cpp:9-20."""
+    return _decode.paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal, q_offset,
+                                kv_format="bf16" if k_pool.dtype == torch.bfloat16 else "f16", **kw)
+
+
+def fp8_forward(q, k_pool, v_pool, block_table, page_size, n_k, scale_k, scale_v, scale, causal=False,
+                q_offset=0, **kw):
+    """kernels/v9_fp8/binding.cpp:9-23.  `scale_k` / `scale_v` are floats (per tensor, the reference
+    layout) or float32 tensors [num_blocks, page_size, H_kv] (one scale per token per head)."""
+    if isinstance(scale_k, torch.Tensor) and scale_k.numel() > 1:
+        return _decode.paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal, q_offset,
+                                    kv_format="e4m3", k_token_scale=scale_k, v_token_scale=scale_v, **kw)
+    return _decode.paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal, q_offset,
+                                kv_format="e4m3", scale_k=float(scale_k), scale_v=float(scale_v), **kw)
+
+
+def nvfp4_forward(q, k_pool, k_scale, v_pool, v_scale, block_table, page_size, n_k, scale_k, scale_v, scale,
+                  causal=False, q_offset=0, **kw):
+    """kernels/v10_nvfp4/binding.cpp."""
+    return _decode.paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal, q_offset,
+                                kv_format="nvfp4", k_micro=k_scale, v_micro=v_scale,
+                                scale_k=float(scale_k), scale_v=float(scale_v), **kw)

@@ -1,0 +1,74 @@
+"""Paged-KV attention entry points — the import surface of the reference's fa_kernels/paged.py
+(same names, argument order and meaning), running on the B200 kernels of libfa_b200.so.
+
+Shapes (fa_kernels/paged.py:12-24 of the reference):
+    q           : [B, H_q, N_q, d]                     CUDA tensor (decode: N_q = 1)
+    k_pool      : [num_blocks, page_size, H_kv, d]     physical KV pool
+    v_pool      : [num_blocks, page_size, H_kv, d]
+    block_table : [B, n_logical] int32                 block_table[b][lb] -> physical block
+    n_k         : logical KV length attended this step; an int (the reference contract) or one
+                  length per sequence (list / tensor of B ints)
+
+Keyword-only additions to every attention call: `out_dtype` (default float32 as in the reference),
+`return_lse` (also return the log-sum-exp [B, H_q, N_q]).
+"""
+
+from __future__ import annotations
+
+DEFAULT_PAGED_BACKEND = "v7_paged"
+DEFAULT_GQA_BACKEND = "v8_gqa"
+DEFAULT_FP8_BACKEND = "v9_fp8"
+DEFAULT_NVFP4_BACKEND = "v10_nvfp4"
+DEFAULT_MLA_BACKEND = "v11_mla"
+DEFAULT_MLA_TC_BACKEND = "v12_mla_tc"
+
+_E4M3_MAX = 448.0
+_NVFP4_BLOCK = 16
+_E2M1_MAX = 6.0
+_E2M1_LEVELS = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+_E2M1_MIDPOINTS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+
+
+def _default_scale(q, scale):
+    return 1.0 / (q.shape[-1] ** 0.5) if scale is None else scale
+
+
+def paged_attention(q, k_pool, v_pool, block_table, page_size, n_k, *, scale=None, causal=False,
+                    q_offset=0, backend=DEFAULT_PAGED_BACKEND, **kw):
+    """Paged-KV attention (reference fa_kernels/paged.py:215-234).  `causal` masks key j when
+    j > query_i + q_offset; at decode set q_offset = n_k - N_q."""
+    from .dispatch import get_backend
+    module = get_backend(backend)
+    return module.forward(q, k_pool, v_pool, block_table, int(page_size), n_k,
+                          _default_scale(q, scale), causal, q_offset, **kw)
+
+
+def gqa_attention(q, k_pool, v_pool, block_table, page_size, n_k, *, scale=None, causal=False,
+                  q_offset=0, backend=DEFAULT_GQA_BACKEND, **kw):
+    """GQA M-packed paged decode (reference fa_kernels/paged.py:379-402): the pool has H_kv heads, q has
+    H_q = G * H_kv; KV head h serves query heads [h*G, h*G + G)."""
+    from .dispatch import get_backend
+    module = get_backend(backend)
+    return module.forward(q, k_pool, v_pool, block_table, int(page_size), n_k,
+                          _default_scale(q, scale), causal, q_offset, **kw)
+
+
+def fp8_attention(q, k_pool, v_pool, block_table, page_size, n_k, scale_k, scale_v, *, scale=None,
+                  causal=False, q_offset=0, backend=DEFAULT_FP8_BACKEND, **kw):
+    """FP8 E4M3 KV-cache GQA decode (reference fa_kernels/paged.py:237-260).  Pools are uint8 E4M3
+    bytes; `scale_k` / `scale_v` are the per-tensor dequant scales, or float32 tensors
+    [num_blocks, page_size, H_kv] holding one scale per token per head."""
+    from .dispatch import get_backend
+    module = get_backend(backend)
+    return module.forward(q, k_pool, v_pool, block_table, int(page_size), n_k, scale_k, scale_v,
+                          _default_scale(q, scale), causal, q_offset, **kw)
+
+
+def nvfp4_attention(q, k_pack, k_micro, v_pack, v_micro, block_table, page_size, n_k, scale_k, scale_v, *,
+                    scale=None, causal=False, q_offset=0, backend=DEFAULT_NVFP4_BACKEND, **kw):
+    """NVFP4 KV-cache GQA decode (reference fa_kernels/paged.py:263-284): packed E2M1 nibbles
+    [.., d/2] + E4M3 micro-scales [.., d/16] + one fp32 scale per tensor."""
+    from .dispatch import get_backend
+    module = get_backend(backend)
+    return module.forward(q, k_pack, k_micro, v_pack, v_micro, block_table, int(page_size), n_k,
+                          float(scale_k), float(scale_v), _default_scale(q, scale), causal, q_offset, **kw)

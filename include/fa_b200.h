@@ -1,0 +1,158 @@
+/*
+ * fa_b200 — C ABI of the B200 (sm_100a) attention library.
+ *
+ * One shared library, `libfa_b200.so`, replaces the per-kernel JIT modules that the reference
+ * project loads through bindings/load.py:107-131 (`build_kernel(name)` -> pybind module with a
+ * `.forward(...)`).  Each entry point below names the reference `forward` it stands in for.
+ *
+ * Conventions
+ *   - every function returns an int status (FA_OK == 0); `fa_last_error()` gives the text of the last
+ *     failure on the calling thread.  Nothing throws, nothing calls exit.
+ *   - pointers marked "device" are CUDA device pointers on the current device; "host" are ordinary
+ *     host pointers.  Tensors are contiguous row-major in the layouts stated.
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*); no entry point synchronises and
+ *     none allocates device memory: scratch ("workspace") is supplied by the caller, sized by the
+ *     matching *_workspace_bytes query.
+ */
+#ifndef FA_B200_H
+#define FA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FA_API __attribute__((visibility("default")))
+#else
+#define FA_API
+#endif
+
+enum fa_status {
+  FA_OK = 0,
+  FA_ERR_INVALID = 1,      /* bad argument (shape, dtype, null pointer) */
+  FA_ERR_UNSUPPORTED = 2,  /* valid request this build has no kernel for (e.g. head_dim) */
+  FA_ERR_CUDA = 3,         /* a CUDA runtime / driver call failed */
+  FA_ERR_WORKSPACE = 4     /* workspace too small */
+};
+
+enum fa_dtype {
+  FA_F16 = 0,
+  FA_BF16 = 1,
+  FA_F32 = 2,
+  FA_E4M3 = 3,   /* uint8 FP8 E4M3 bytes (fa_kernels/paged.py:94-109) */
+  FA_NVFP4 = 4   /* packed E2M1 nibbles + one E4M3 micro-scale per 16 elements (paged.py:136-170) */
+};
+
+FA_API const char* fa_last_error(void);
+FA_API int fa_version(void);
+/* Number of SMs of the current device (cached per device). */
+FA_API int fa_device_sm_count(int* sm_count);
+
+/* ------------------------------------------------------------------------------------------------
+ * Paged GQA decode (split-KV, M-packed query heads, fused LSE merge).
+ * Replaces `forward` of kernels/v7_paged/binding.cpp, kernels/v8_gqa_ss/binding.cpp:9-20,
+ * kernels/v9_fp8/binding.cpp:9-23 and kernels/v10_nvfp4/binding.cpp — i.e. the calls made at
+ * fa_kernels/paged.py:232-234, 258-260, 282-284, 400-402.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* One unit of work: keys [k_begin, k_end) of sequence b.  Produced by fa_decode_plan on the host and
+ * consumed by the kernel from device memory (the caller copies it). 8 x int32. */
+typedef struct fa_decode_item {
+  int32_t b;
+  int32_t k_begin;
+  int32_t k_end;
+  int32_t slot_base;  /* first partial-result slot of sequence b */
+  int32_t n_split;    /* number of key ranges sequence b was cut into */
+  int32_t split;      /* index of this range within the sequence */
+  int32_t pad0;
+  int32_t pad1;
+} fa_decode_item;
+
+/* Host-side split planner (no CUDA calls).  The reference picks ONE split count for the whole batch
+ * from a single n_k (choose_splits, kernels/v8_gqa_ss/gqa_ss_attention.cu:248-259); this planner
+ * cuts each sequence by its own length so that the grid is a multiple of the SM count's worth of
+ * similar-sized ranges, longest first.
+ *   seq_lens_host : host int32[B] per-sequence key counts, or NULL to use n_k for every sequence
+ *   rows          : packed query rows per KV head = (H_q / H_kv) * N_q
+ *   chunk_hint    : 0 = choose; otherwise the target keys per range (rounded to a multiple of 64)
+ *   items         : host output, capacity max_items
+ *   n_items       : output, number of ranges (each range owns one partial-result slot)
+ *   max_range_keys: output, the longest range in keys */
+FA_API int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int H_kv, int rows, int page_size,
+                   int num_sms, int chunk_hint, fa_decode_item* items, int max_items,
+                   int* n_items, int* max_range_keys);
+/* Upper bound on the number of items fa_decode_plan can emit for these arguments. */
+FA_API int fa_decode_plan_max_items(const int32_t* seq_lens_host, int n_k, int B, int page_size);
+
+typedef struct fa_decode_args {
+  /* queries: device, [B, H_q, N_q, D], dtype FA_F16 or FA_BF16 (FA_BF16 only with FA_BF16 pools) */
+  const void* q;
+  int q_dtype;
+  /* pools: device, [num_blocks, page_size, H_kv, DX].  DX = D (f16/bf16/e4m3) or D/2 (nvfp4). */
+  const void* k_pool;
+  const void* v_pool;
+  int kv_dtype;
+  /* NVFP4 only: device uint8 [num_blocks, page_size, H_kv, D/16] E4M3 micro-scales */
+  const void* k_micro;
+  const void* v_micro;
+  /* per-tensor dequant scales (1.0 for f16/bf16) — `scale_k`, `scale_v` of paged.py:237,263 */
+  float k_scale;
+  float v_scale;
+  /* E4M3 only, optional: device float32 [num_blocks, page_size, H_kv] per-token-per-head scales that
+   * multiply k_scale / v_scale.  NULL = per-tensor only (the reference layout). */
+  const float* k_token_scale;
+  const float* v_token_scale;
+  /* device int32 [B, n_logical] */
+  const int32_t* block_table;
+  int n_logical;
+  int num_blocks;
+  int page_size;
+  int B, H_q, H_kv, N_q, D;
+  float softmax_scale;
+  int causal;          /* key j is masked when j > i_q + q_offset (v7_paged/paged_attention.cu:138) */
+  int q_offset;
+  /* optional device int32[B]: per-sequence q_offset overriding the scalar */
+  const int32_t* q_offsets;
+  /* plan */
+  const fa_decode_item* items;  /* device copy of the planner output */
+  int n_items;
+  int n_slots;         /* n_items, or 0 when no sequence is split (no partial storage is used) */
+  int max_range_keys;  /* from fa_decode_plan */
+  /* outputs: device, [B, H_q, N_q, D] in out_dtype (FA_F32 is the reference behaviour, FA_F16/FA_BF16
+   * are accepted); lse optional float32 [B, H_q, N_q] (natural log), may be NULL */
+  void* out;
+  int out_dtype;
+  float* lse;
+  /* scratch: partial results of split sequences (fa_decode_workspace_bytes; contents need no
+   * initialisation) and arrival counters (fa_decode_counters_len int32 words, zero before the first
+   * call; the kernel leaves them zero again, the last word collects error flags).  Neither may be
+   * shared by decode calls that overlap in time. */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* counters;
+  size_t counters_len;
+  void* stream;
+  int variant;         /* 0 = default kernel configuration; other values select tuning variants */
+} fa_decode_args;
+
+FA_API size_t fa_decode_workspace_bytes(int n_slots, int H_q, int N_q, int D);
+FA_API size_t fa_decode_counters_len(int B, int H_q, int H_kv, int N_q);
+FA_API int fa_paged_decode_fwd(const fa_decode_args* args);
+
+/* ------------------------------------------------------------------------------------------------
+ * Merge of normalised partial outputs over disjoint key ranges (the algebra of the reference merge
+ * kernels, e.g. kernels/v8_gqa_ss/gqa_ss_attention.cu:209-231, with (m, l) folded into LSE).
+ * Used after the all-gather of per-GPU partials when one sequence's keys are spread over GPUs.
+ *   o_parts  : device float32 [n_parts, rows, D]     lse_parts : device float32 [n_parts, rows]
+ *   out      : device [rows, D] in out_dtype          lse_out   : optional float32 [rows]
+ * ---------------------------------------------------------------------------------------------- */
+FA_API int fa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int64_t rows, int D,
+                      void* out, int out_dtype, float* lse_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H */
