@@ -58,6 +58,7 @@ struct DecodeParams {
   int n_logical, num_blocks, page_size, page_shift;
   int B, H_q, H_kv, N_q, G, M;
   int causal, q_offset, out_dtype, bt_cap;
+  int n_items, head_major;
 };
 
 template <int D, int FMT>
@@ -114,8 +115,10 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
   const int warp = tid >> 5, lane = tid & 31;
   const int g4 = lane >> 2, c = lane & 3;
 
-  const int item_idx = blockIdx.x / p.H_kv;
-  const int h_kv = blockIdx.x - item_idx * p.H_kv;
+  // consecutive CTAs serve the KV heads of one key range, so that the 8 x 256-byte head rows of a
+  // token (one contiguous 2 KB line of the pool) are fetched by CTAs that run at the same time
+  const int item_idx = p.head_major ? (int)(blockIdx.x % p.n_items) : (int)(blockIdx.x / p.H_kv);
+  const int h_kv = p.head_major ? (int)(blockIdx.x / p.n_items) : (int)(blockIdx.x - item_idx * p.H_kv);
   const int m0 = blockIdx.y * kRowTile;
   const fa_decode_item it = p.items[item_idx];
   const int b = it.b;
@@ -650,16 +653,23 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     FA_CHECK_ARG(len >= 0, "fa_decode_plan: negative sequence length at b=%d", b);
     total += len;
   }
-  // ranges of ~equal size, enough of them for ~8 waves of 2 CTAs per SM, never shorter than 256 keys
+  // Every range pays a fixed start-up (metadata, block table, pipeline fill), so sequences are cut only
+  // when there are fewer (sequence, head, row tile) units than CTA slots (2 per SM); then ~2 ranges
+  // per slot, never shorter than 256 keys.
   const int64_t max_chunk = (int64_t)(kMaxPages - 1) * page_size / kTN * kTN;
   FA_CHECK_ARG(max_chunk >= kTN, "fa_decode_plan: page_size too small");
   int64_t chunk;
   if (chunk_hint > 0) {
     chunk = chunk_hint;
   } else {
-    const int64_t target_ctas = (int64_t)num_sms * 2 * 8;
-    chunk = (total * H_kv * row_tiles + target_ctas - 1) / target_ctas;
-    chunk = std::max<int64_t>(chunk, 256);
+    const int64_t slots = (int64_t)num_sms * 2;
+    const int64_t units = (int64_t)B * H_kv * row_tiles;
+    if (units >= slots) {
+      chunk = max_chunk;
+    } else {
+      chunk = (total * H_kv * row_tiles + 2 * slots - 1) / (2 * slots);
+      chunk = std::max<int64_t>(chunk, 256);
+    }
   }
   chunk = (chunk + kTN - 1) / kTN * kTN;
   chunk = std::min(chunk, max_chunk);
@@ -775,6 +785,7 @@ extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
   p.page_shift = ((a->page_size & (a->page_size - 1)) == 0) ? __builtin_ctz((unsigned)a->page_size) : -1;
   p.B = a->B; p.H_q = a->H_q; p.H_kv = a->H_kv; p.N_q = a->N_q; p.G = G; p.M = M;
   p.causal = a->causal; p.q_offset = a->q_offset; p.out_dtype = a->out_dtype;
+  p.n_items = a->n_items; p.head_major = (a->variant == 2);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
 
 #define FA_LAUNCH(D_, F_, NS_, MB_) return launch_decode<D_, F_, NS_, MB_>(p, a->n_items, row_tiles, st)

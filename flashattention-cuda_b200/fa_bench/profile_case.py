@@ -1,0 +1,46 @@
+"""Run a few launches of one workload's kernel so that a profiler can be attached to a small, bounded
+process (the role of the reference's single-shape loop, bench/regime.py:268-287).
+
+    python flashattention-cuda_b200/fa_bench/profile_case.py --workload paged_gqa_decode_fp16 --launches 4
+
+Prints the CUDA-event time of every launch.  The L2 is flushed before each launch.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+
+import torch  # noqa: E402
+
+
+def make_step(name, device, batch=None):
+    from fa_bench import workloads
+    from fa_kernels import gqa_attention
+    if name == "paged_gqa_decode_fp16":
+        w = workloads.paged_gqa_decode(device, batch=batch or 64)
+        fn = lambda: gqa_attention(w["q"], w["k_pool"], w["v_pool"], w["block_table"], w["page_size"], w["seq_lens"],
+                                   out_dtype=torch.float16)
+        return fn, w["kv_bytes"]
+    raise SystemExit(f"unknown workload {name!r}")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="paged_gqa_decode_fp16")
+    ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=None)
+    args = ap.parse_args()
+    from fa_bench import timing
+    dev = torch.device("cuda:0")
+    fn, nbytes = make_step(args.workload, dev, args.batch)
+    for i, ms in enumerate(timing.time_cuda(fn, warmup=1, iters=args.launches - 1, device=dev)):
+        print(f"launch {i + 1}: {ms * 1e3:.1f} us  {nbytes / ms / 1e6:.0f} GB/s")
+
+
+if __name__ == "__main__":
+    main()

@@ -159,3 +159,21 @@ def test_config1_cpu_plumbing(golden):
     np.testing.assert_allclose(out.reshape(-1)[::stride], g["out_sample"], atol=2e-6, rtol=1e-5)
     np.testing.assert_allclose(np.abs(out).sum(), float(g["out_abs_sum"]), rtol=1e-6)
     assert lse.shape == (2, 8, 512) and np.isfinite(lse).all()
+
+
+def test_torch_cpu_port_matches_reference_outputs(golden):
+    import torch
+    from oracle import cpu_reference as R
+    g = golden("sdpa.npz")
+    t = lambda a: torch.from_numpy(a)
+    np.testing.assert_allclose(R.sdpa_reference(t(g["q"]), t(g["k"]), t(g["v"]), causal=True).numpy(),
+                               g["out_causal"], atol=1e-6, rtol=1e-6)
+    np.testing.assert_allclose(R.sdpa_reference_gqa(t(g["qd"]), t(g["kg"]), t(g["vg"])).numpy(),
+                               g["out_gqa_decode"], atol=1e-6, rtol=1e-6)
+    m = golden("mla.npz")
+    np.testing.assert_allclose(
+        R.sdpa_reference_mla_dequantised(t(m["q"]), t(m["lat_hat"]), int(m["kv_lora_rank"])).numpy(),
+        m["out"], atol=1e-6, rtol=1e-6)
+    p = golden("paged.npz")
+    dense = R.gather_dense(t(p["k_pool"]), t(p["block_table"])[1], int(p["page_size"]), int(p["n_k"]))
+    np.testing.assert_array_equal(dense[0].numpy(), p["k"][1])
