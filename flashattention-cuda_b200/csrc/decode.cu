@@ -807,6 +807,51 @@ extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
 #undef FA_LAUNCH
 }
 
+// ---- decode without any caller-supplied or allocated scratch ---------------------------------------
+// Scratch of fa_paged_decode_fwd_static: the first kStaticCounterWords int32 words are the arrival
+// counters, the rest holds the partial results of split sequences.  The array lives in the library's
+// device image, so every GPU that loads the library carries these bytes until the process exits.
+namespace {
+constexpr size_t kStaticCounterWords = 16384;
+constexpr size_t kStaticScratchBytes = FA_DECODE_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_ptr[kMaxDevices] = {nullptr};   // device address per device ordinal
+}  // namespace
+
+extern "C" int fa_paged_decode_fwd_static(const fa_decode_args* a) {
+  FA_CHECK_ARG(a != nullptr, "fa_paged_decode_fwd_static: null args");
+  int dev = 0;
+  FA_CUDA_OK(cudaGetDevice(&dev));
+  FA_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the device address has to be asked for, once
+    // per device, with that device current.
+    void* ptr = nullptr;
+    FA_CUDA_OK(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+    g_static_scratch_ptr[dev] = static_cast<unsigned char*>(ptr);
+  }
+  const size_t n_counters = fa_decode_counters_len(a->B, a->H_q, a->H_kv, a->N_q);
+  if (n_counters > kStaticCounterWords)
+    return fail(FA_ERR_WORKSPACE,
+                "fa_paged_decode_fwd_static: %zu (sequence, head, row tile) counters exceed the built-in %zu; "
+                "use fa_paged_decode_fwd with caller scratch", n_counters, kStaticCounterWords);
+  const size_t part_cap = kStaticScratchBytes - kStaticCounterWords * sizeof(int32_t);
+  const size_t part_need = fa_decode_workspace_bytes(a->n_slots, a->H_q, a->N_q, a->D);
+  if (part_need > part_cap)
+    return fail(FA_ERR_WORKSPACE,
+                "fa_paged_decode_fwd_static: partial results need %zu B, the built-in scratch holds %zu B; "
+                "use fa_paged_decode_fwd with caller scratch", part_need, part_cap);
+  fa_decode_args b = *a;
+  b.counters = reinterpret_cast<int32_t*>(g_static_scratch_ptr[dev]);
+  b.counters_len = kStaticCounterWords;
+  b.workspace = g_static_scratch_ptr[dev] + kStaticCounterWords * sizeof(int32_t);
+  b.workspace_bytes = part_cap;
+  // The array keeps whatever the previous call left; the counters have to start at zero.
+  FA_CUDA_OK(cudaMemsetAsync(b.counters, 0, n_counters * sizeof(int32_t), reinterpret_cast<cudaStream_t>(a->stream)));
+  return fa_paged_decode_fwd(&b);
+}
+
 extern "C" int fa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int64_t rows, int D,
                                  void* out, int out_dtype, float* lse_out, void* stream) {
   FA_CHECK_ARG(o_parts && lse_parts && out, "fa_merge_partials: null pointer");

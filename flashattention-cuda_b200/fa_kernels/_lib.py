@@ -69,7 +69,9 @@ def _declare(lib):
 
 
 # entry points declared by later sections of include/fa_b200.h (argtypes filled in when present)
-_OPTIONAL: dict = {}
+_OPTIONAL: dict = {
+    "fa_paged_decode_fwd_static": [C.POINTER(DecodeArgs)],
+}
 
 
 def load():

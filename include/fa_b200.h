@@ -142,6 +142,28 @@ FA_API size_t fa_decode_workspace_bytes(int n_slots, int H_q, int N_q, int D);
 FA_API size_t fa_decode_counters_len(int B, int H_q, int H_kv, int N_q);
 FA_API int fa_paged_decode_fwd(const fa_decode_args* args);
 
+/* Same computation as fa_paged_decode_fwd for callers that have no device memory to give and cannot
+ * obtain any.  (This entry point has no counterpart in the reference, whose host functions allocate
+ * their outputs and workspaces with torch on every call.)  Two kinds of host are meant: an inference
+ * server that hands the whole device to its KV-cache pool at start-up, so that a later cudaMalloc
+ * fails or fragments the pool; and a plugin host that passes the plugin its input and output buffers
+ * but no allocator, where a cudaMalloc from inside the plugin would also stall the device, because
+ * cudaMalloc synchronises it.
+ *
+ * The `workspace`, `workspace_bytes`, `counters` and `counters_len` fields of `args` are ignored: the
+ * scratch is a fixed array of FA_DECODE_STATIC_SCRATCH_BYTES inside the library's device image.  The
+ * call allocates nothing (no cudaMalloc / cudaFree, no library routine that allocates).
+ *   - Limits: at most 16384 (sequence, KV head, 16-row tile) units per call, and the partial results of
+ *     split sequences (fa_decode_workspace_bytes) must fit in the remaining bytes; beyond either limit
+ *     the call returns FA_ERR_WORKSPACE and launches nothing.
+ *   - The first call on each device looks up the array's device address; make that first call outside
+ *     any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
+ *     streams, different threads) race on it and give wrong results.  Serialise them, or use
+ *     fa_paged_decode_fwd with one scratch buffer per concurrent call. */
+#define FA_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
+FA_API int fa_paged_decode_fwd_static(const fa_decode_args* args);
+
 /* ------------------------------------------------------------------------------------------------
  * Merge of normalised partial outputs over disjoint key ranges (the algebra of the reference merge
  * kernels, e.g. kernels/v8_gqa_ss/gqa_ss_attention.cu:209-231, with (m, l) folded into LSE).
