@@ -72,3 +72,27 @@ def nvfp4_attention(q, k_pack, k_micro, v_pack, v_micro, block_table, page_size,
     module = get_backend(backend)
     return module.forward(q, k_pack, k_micro, v_pack, v_micro, block_table, int(page_size), n_k,
                           float(scale_k), float(scale_v), _default_scale(q, scale), causal, q_offset, **kw)
+
+
+# ---- layout builders and quantisers (reference fa_kernels/paged.py:48-212, 287-309) ------------------
+# Thin lazy forwards so that `import fa_kernels` needs neither torch nor the CUDA library.
+def _fwd(name):
+    def call(*args, **kwargs):
+        from . import _formats
+        return getattr(_formats, name)(*args, **kwargs)
+    call.__name__ = name
+    call.__doc__ = f"See fa_kernels._formats.{name} (GPU implementation of the reference helper of the same name)."
+    return call
+
+
+build_paged_kv = _fwd("build_paged_kv")
+build_paged_kv_fp8 = _fwd("build_paged_kv_fp8")
+build_paged_kv_fp8_per_token = _fwd("build_paged_kv_fp8_per_token")
+build_paged_kv_nvfp4 = _fwd("build_paged_kv_nvfp4")
+build_paged_kv_mla = _fwd("build_paged_kv_mla")
+quantize_fp8_e4m3 = _fwd("quantize_fp8_e4m3")
+quantize_fp8_e4m3_per_token = _fwd("quantize_fp8_e4m3_per_token")
+dequantize_fp8_e4m3 = _fwd("dequantize_fp8_e4m3")
+quantize_nvfp4 = _fwd("quantize_nvfp4")
+dequantize_nvfp4 = _fwd("dequantize_nvfp4")
+paged_gather = _fwd("paged_gather")

@@ -174,6 +174,35 @@ FA_API int fa_paged_decode_fwd_static(const fa_decode_args* args);
 FA_API int fa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int64_t rows, int D,
                       void* out, int out_dtype, float* lse_out, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * KV-cache formats and the paged layout (bit-exact with the reference's torch functions).
+ * ---------------------------------------------------------------------------------------------- */
+
+/* FP8 E4M3 quantise — `quantize_fp8_e4m3`, fa_kernels/paged.py:94-109.
+ *   per_row == 0 : one scale for the tensor, scale = float32(max(amax, 1e-12) / 448) -> scales[0]
+ *   per_row  > 0 : one scale per row of per_row elements (per token per head) -> scales[n / per_row]
+ *   x: device f32/f16/bf16 [n]; out: device uint8 [n]; scratch4: device, 4 bytes (per-tensor mode). */
+FA_API int fa_quantize_fp8_e4m3(const void* x, int x_dtype, int64_t n, int per_row, uint8_t* out, float* scales,
+                                void* scratch4, void* stream);
+/* `dequantize_fp8_e4m3`, fa_kernels/paged.py:112-118: out[i] = e4m3(bytes[i]) * scale (or row_scales). */
+FA_API int fa_dequantize_fp8_e4m3(const uint8_t* bytes, int64_t n, float scale, const float* row_scales, int per_row,
+                                  float* out, void* stream);
+/* NVFP4 quantise — `quantize_nvfp4`, fa_kernels/paged.py:136-170.  n elements, the last dimension a
+ * multiple of 16; packed: uint8 [n/2] (low nibble = even element), micro: uint8 [n/16] E4M3,
+ * scale_out: device float32[1] = max(amax, 1e-12) / (6 * 448). */
+FA_API int fa_quantize_nvfp4(const void* x, int x_dtype, int64_t n, uint8_t* packed, uint8_t* micro, float* scale_out,
+                             void* scratch4, void* stream);
+/* `dequantize_nvfp4`, fa_kernels/paged.py:173-189. */
+FA_API int fa_dequantize_nvfp4(const uint8_t* packed, const uint8_t* micro, int64_t n, float scale, float* out, void* stream);
+/* Dense [B, H, N, row_bytes] -> pool [num_blocks, page_size, H, row_bytes] with
+ * pool[block_table[b][j / page], j % page] = dense[b, :, j]; the tail of the last page is zeroed.
+ * The scatter of `build_paged_kv`, fa_kernels/paged.py:75-88 (the permutation is the caller's). */
+FA_API int fa_paged_scatter(const void* dense, void* pool, const int32_t* block_table, int B, int H, int N, int row_bytes,
+                            int page_size, int n_logical, int num_blocks, void* stream);
+/* The inverse: the gather every kernel performs (kernels/v7_paged/paged_attention.cu:118-131). */
+FA_API int fa_paged_gather(const void* pool, void* dense, const int32_t* block_table, int B, int H, int N, int row_bytes,
+                           int page_size, int n_logical, int num_blocks, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,148 @@
+"""Bit-exact parity of the GPU quantisers / pagers with the oracle and with the committed fixtures
+(which came from the reference's own quantisers): FP8 E4M3 per tensor and per token, NVFP4 pack and
+micro-scales, paged scatter / gather.  Every comparison is exact equality."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _np(t):
+    return t.cpu().numpy()
+
+
+def test_fp8_per_tensor_fixture(golden):
+    from fa_kernels.paged import dequantize_fp8_e4m3, quantize_fp8_e4m3
+    g = golden("quant_fp8.npz")
+    b, s = quantize_fp8_e4m3(torch.from_numpy(g["x"]).cuda())
+    assert s == float(g["scale"])
+    np.testing.assert_array_equal(_np(b), g["bytes"])
+    np.testing.assert_array_equal(_np(dequantize_fp8_e4m3(b, s)), g["dequant"])
+
+
+def test_e4m3_cast_on_every_probe(golden):
+    """The kernel's float->E4M3 rounding on the tie / range-edge probes: quantise with scale exactly 1
+    by planting amax = 448 in the tensor."""
+    from fa_kernels.paged import quantize_fp8_e4m3
+    g = golden("e4m3_codec.npz")
+    probes, enc = g["probes"], g["encoded"]
+    keep = np.abs(probes) <= 448.0
+    x = np.concatenate([probes[keep], np.array([448.0], np.float32)]).astype(np.float32)
+    b, s = quantize_fp8_e4m3(torch.from_numpy(x).cuda())
+    assert s == 1.0
+    np.testing.assert_array_equal(_np(b)[:-1], enc[keep])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_fp8_random_and_per_token(dtype):
+    from fa_kernels.paged import dequantize_fp8_e4m3, quantize_fp8_e4m3, quantize_fp8_e4m3_per_token
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(2, 8, 301, 128, generator=g) * 2.5)
+    x[..., 7] *= 10.0
+    x[0, 0, 5] = 0.0                                  # an all-zero row -> scale clamps at 1e-12 / 448
+    x = x.to(dtype)
+    xn = x.float().numpy()
+    b, s = quantize_fp8_e4m3(x.cuda())
+    rb, rs = O.quantize_fp8_e4m3(xn)
+    assert s == rs
+    np.testing.assert_array_equal(_np(b), rb)
+    bt, st = quantize_fp8_e4m3_per_token(x.cuda())
+    rbt, rst = O.quantize_fp8_e4m3_per_token(xn)
+    np.testing.assert_array_equal(_np(st), rst)
+    np.testing.assert_array_equal(_np(bt), rbt)
+    np.testing.assert_array_equal(_np(dequantize_fp8_e4m3(bt, st)), O.e4m3_decode(rbt) * rst[..., None])
+
+
+def test_nvfp4_fixture(golden):
+    from fa_kernels.paged import dequantize_nvfp4, quantize_nvfp4
+    g = golden("quant_nvfp4.npz")
+    p, m, s = quantize_nvfp4(torch.from_numpy(g["x"]).cuda())
+    assert s == float(g["scale"])
+    np.testing.assert_array_equal(_np(m), g["micro"])
+    np.testing.assert_array_equal(_np(p), g["packed"])
+    np.testing.assert_array_equal(_np(dequantize_nvfp4(p, m, s)), g["dequant"])
+
+
+@pytest.mark.parametrize("d", [64, 128, 576])
+def test_nvfp4_random_with_outliers(d):
+    from fa_kernels.paged import dequantize_nvfp4, quantize_nvfp4
+    g = torch.Generator().manual_seed(d)
+    x = torch.randn(2, 3, 257, d, generator=g)
+    x[..., 5] *= 10.0
+    x[1, 2, 100, 16:32] = 0.0
+    p, m, s = quantize_nvfp4(x.cuda())
+    rp, rm, rs = O.quantize_nvfp4(x.numpy())
+    assert s == rs
+    np.testing.assert_array_equal(_np(m), rm)
+    np.testing.assert_array_equal(_np(p), rp)
+    np.testing.assert_array_equal(_np(dequantize_nvfp4(p, m, s)), O.dequantize_nvfp4(rp, rm, rs))
+
+
+def test_pager_fixture_and_roundtrip(golden):
+    from fa_kernels._formats import paged_gather, paged_scatter
+    g = golden("paged.npz")
+    bt = torch.from_numpy(g["block_table"]).cuda()
+    page = int(g["page_size"])
+    kp = paged_scatter(torch.from_numpy(g["k"]).cuda(), page, bt)
+    np.testing.assert_array_equal(_np(kp), g["k_pool"])
+    np.testing.assert_array_equal(_np(paged_gather(kp, bt, page, int(g["n_k"]))), g["k"])
+
+
+@pytest.mark.parametrize("dtype,dx", [(torch.float16, 128), (torch.uint8, 64), (torch.uint8, 8), (torch.float32, 1),
+                                      (torch.uint8, 3)])
+def test_build_paged_kv_matches_oracle(dtype, dx):
+    from fa_kernels.paged import build_paged_kv, paged_gather
+    g = torch.Generator().manual_seed(9)
+    B, H, N, page = 3, 2, 333, 16
+    if dtype == torch.uint8:
+        k = torch.randint(0, 256, (B, H, N, dx), generator=g, dtype=torch.int32).to(torch.uint8)
+        v = torch.randint(0, 256, (B, H, N, dx), generator=g, dtype=torch.int32).to(torch.uint8)
+    else:
+        k = torch.randn(B, H, N, dx, generator=g).to(dtype)
+        v = torch.randn(B, H, N, dx, generator=g).to(dtype)
+    kp, vp, bt, n_k = build_paged_kv(k.cuda(), v.cuda(), page, seed=4)
+    assert n_k == N and bt.dtype == torch.int32 and tuple(bt.shape) == (B, 21)
+    perm = _np(bt).reshape(-1)
+    assert sorted(perm.tolist()) == list(range(B * 21))          # a permutation of the physical pages
+    rk, rv, rbt, _ = O.build_paged_kv(k.numpy(), v.numpy(), page, perm)
+    np.testing.assert_array_equal(_np(kp), rk)
+    np.testing.assert_array_equal(_np(vp), rv)
+    np.testing.assert_array_equal(_np(paged_gather(vp, bt, page, N)), v.numpy())
+    # unshuffled: identity table
+    _, _, bt0, _ = build_paged_kv(k.cuda(), v.cuda(), page, shuffle=False)
+    assert _np(bt0).reshape(-1).tolist() == list(range(B * 21))
+
+
+def test_builders_feed_the_decode_kernels():
+    """End to end through the reference-shaped helpers: build_paged_kv_fp8 / _nvfp4 -> attention."""
+    from fa_kernels import fp8_attention, nvfp4_attention
+    from fa_kernels.paged import build_paged_kv_fp8, build_paged_kv_fp8_per_token, build_paged_kv_nvfp4
+    from helpers import assert_close
+    g = torch.Generator().manual_seed(12)
+    B, H_kv, G, N, d, page = 2, 2, 4, 1500, 128, 64
+    q = torch.randn(B, G * H_kv, 1, d, generator=g).half()
+    k = torch.randn(B, H_kv, N, d, generator=g)
+    v = torch.randn(B, H_kv, N, d, generator=g)
+    qn, kn, vn = q.float().numpy(), k.numpy(), v.numpy()
+    kp, vp, bt, n_k, sk, sv = build_paged_kv_fp8(k.cuda(), v.cuda(), page, seed=1)
+    out = fp8_attention(q.cuda(), kp, vp, bt, page, n_k, sk, sv)
+    kb, rsk = O.quantize_fp8_e4m3(kn)
+    vb, rsv = O.quantize_fp8_e4m3(vn)
+    assert (sk, sv) == (rsk, rsv)
+    assert_close(out, O.gqa_attention_ref(qn, O.dequantize_fp8_e4m3(kb, sk), O.dequantize_fp8_e4m3(vb, sv)), what="fp8")
+    kp, vp, bt, n_k, ksp, vsp = build_paged_kv_fp8_per_token(k.cuda(), v.cuda(), page, seed=1)
+    out = fp8_attention(q.cuda(), kp, vp, bt, page, n_k, ksp, vsp)
+    kb, ks = O.quantize_fp8_e4m3_per_token(kn)
+    vb, vs = O.quantize_fp8_e4m3_per_token(vn)
+    assert_close(out, O.gqa_attention_ref(qn, O.e4m3_decode(kb) * ks[..., None], O.e4m3_decode(vb) * vs[..., None]),
+                 what="fp8 per token")
+    kp, km, vp, vm, bt, n_k, sk, sv = build_paged_kv_nvfp4(k.cuda(), v.cuda(), page, seed=1)
+    out = nvfp4_attention(q.cuda(), kp, km, vp, vm, bt, page, n_k, sk, sv)
+    assert_close(out, O.gqa_attention_ref(qn, O.dequantize_nvfp4(*O.quantize_nvfp4(kn)), O.dequantize_nvfp4(*O.quantize_nvfp4(vn))),
+                 what="nvfp4")
