@@ -612,18 +612,18 @@ int launch_decode(const DecodeParams& p, int n_items, int row_tiles, cudaStream_
 
 // ---- merge of rank-major partials --------------------------------------------------------------
 __global__ void merge_partials_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
-                                      int n_parts, int64_t rows, int D, void* out, int out_dtype,
-                                      float* lse_out) {
+                                      int n_parts, int64_t rows, int D, int64_t o_stride, int64_t lse_stride,
+                                      void* out, int out_dtype, float* lse_out) {
   const int64_t row = blockIdx.x;
   float mstar = -INFINITY;
-  for (int s = 0; s < n_parts; ++s) mstar = fmaxf(mstar, lse_parts[s * rows + row]);
+  for (int s = 0; s < n_parts; ++s) mstar = fmaxf(mstar, lse_parts[s * lse_stride + row]);
   const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
   float l = 0.f;
-  for (int s = 0; s < n_parts; ++s) l += __expf(lse_parts[s * rows + row] - m_use);
+  for (int s = 0; s < n_parts; ++s) l += __expf(lse_parts[s * lse_stride + row] - m_use);
   for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < n_parts; ++s)
-      acc += __expf(lse_parts[s * rows + row] - m_use) * o_parts[(s * rows + row) * D + dd];
+      acc += __expf(lse_parts[s * lse_stride + row] - m_use) * o_parts[s * o_stride + row * D + dd];
     store_out_dyn(out, out_dtype, row * D + dd, (l > 0.f) ? acc / l : 0.f);
   }
   if (lse_out && threadIdx.x == 0) lse_out[row] = (l > 0.f) ? m_use + __logf(l) : -INFINITY;
@@ -853,14 +853,17 @@ extern "C" int fa_paged_decode_fwd_static(const fa_decode_args* a) {
 }
 
 extern "C" int fa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int64_t rows, int D,
-                                 void* out, int out_dtype, float* lse_out, void* stream) {
+                                 int64_t o_part_stride, int64_t lse_part_stride, void* out, int out_dtype,
+                                 float* lse_out, void* stream) {
   FA_CHECK_ARG(o_parts && lse_parts && out, "fa_merge_partials: null pointer");
   FA_CHECK_ARG(n_parts >= 1 && rows >= 1 && D >= 1, "fa_merge_partials: bad sizes");
   FA_CHECK_ARG(rows <= INT_MAX, "fa_merge_partials: too many rows");
   FA_CHECK_ARG(out_dtype == FA_F32 || out_dtype == FA_F16 || out_dtype == FA_BF16, "out_dtype must be f32/f16/bf16");
+  if (o_part_stride <= 0) o_part_stride = rows * D;
+  if (lse_part_stride <= 0) lse_part_stride = rows;
   const int threads = D >= 256 ? 256 : (D >= 128 ? 128 : 64);
   merge_partials_kernel<<<(unsigned)rows, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      o_parts, lse_parts, n_parts, rows, D, out, out_dtype, lse_out);
+      o_parts, lse_parts, n_parts, rows, D, o_part_stride, lse_part_stride, out, out_dtype, lse_out);
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }

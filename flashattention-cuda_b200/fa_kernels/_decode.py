@@ -90,7 +90,7 @@ def _lens_tuple(n_k, B):
 def paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal=False, q_offset=0, *,
                  kv_format="f16", k_micro=None, v_micro=None, scale_k=1.0, scale_v=1.0,
                  k_token_scale=None, v_token_scale=None, out_dtype=None, return_lse=False,
-                 chunk_hint=0, variant=0):
+                 chunk_hint=0, variant=0, out=None, lse_out=None):
     lib = _lib.load()
     _require(q.is_cuda and k_pool.is_cuda and v_pool.is_cuda and block_table.is_cuda,
              "q, k_pool, v_pool, block_table must be CUDA tensors")
@@ -150,8 +150,17 @@ def paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal=F
     if out_dtype is None:
         out_dtype = torch.float32                       # the reference returns fp32 (gqa_ss_attention.cu:296)
     _require(out_dtype in _TORCH_TO_FA, "out_dtype must be float32, float16 or bfloat16")
-    out = torch.empty((B, H_q, N_q, d), dtype=out_dtype, device=dev)
-    lse = torch.empty((B, H_q, N_q), dtype=torch.float32, device=dev) if return_lse else None
+    if out is not None:            # caller-provided destination (e.g. a slice of a communication buffer)
+        _require(out.is_cuda and out.is_contiguous() and out.numel() == B * H_q * N_q * d and out.dtype == out_dtype,
+                 "out= must be a contiguous CUDA tensor of B*H_q*N_q*d elements in out_dtype")
+    else:
+        out = torch.empty((B, H_q, N_q, d), dtype=out_dtype, device=dev)
+    if lse_out is not None:
+        _require(lse_out.is_cuda and lse_out.is_contiguous() and lse_out.numel() == B * H_q * N_q
+                 and lse_out.dtype == torch.float32, "lse_out= must be a contiguous CUDA float32 tensor of B*H_q*N_q")
+        lse, return_lse = lse_out, True
+    else:
+        lse = torch.empty((B, H_q, N_q), dtype=torch.float32, device=dev) if return_lse else None
 
     q_offsets_t = None
     if isinstance(q_offset, torch.Tensor):
@@ -193,18 +202,23 @@ def paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal=F
 
 
 def merge_partials(o_parts, lse_parts, out_dtype=torch.float32, return_lse=False):
-    """o_parts [S, ..., D] fp32 normalised partial outputs, lse_parts [S, ...] -> merged [..., D]."""
+    """o_parts [S, ..., D] fp32 normalised partial outputs, lse_parts [S, ...] -> merged [..., D].
+
+    The parts may be strided views of one gathered buffer (dim 0 stride arbitrary, the rest dense)."""
     lib = _lib.load()
     _require(o_parts.is_cuda and lse_parts.is_cuda, "partials must be CUDA tensors")
-    o_parts = o_parts.contiguous().float()
-    lse_parts = lse_parts.contiguous().float()
+    _require(o_parts.dtype == torch.float32 and lse_parts.dtype == torch.float32, "partials must be float32")
     S, D = o_parts.shape[0], o_parts.shape[-1]
+    if not (o_parts[0].is_contiguous() and lse_parts[0].is_contiguous()):
+        o_parts, lse_parts = o_parts.contiguous(), lse_parts.contiguous()
     rows = lse_parts[0].numel()
-    _require(o_parts.numel() == S * rows * D and lse_parts.shape[0] == S, "o_parts / lse_parts shapes disagree")
+    _require(o_parts[0].numel() == rows * D and lse_parts.shape[0] == S, "o_parts / lse_parts shapes disagree")
+    o_stride = o_parts.stride(0) if S > 1 else rows * D
+    l_stride = lse_parts.stride(0) if S > 1 else rows
     out = torch.empty(o_parts.shape[1:], dtype=out_dtype, device=o_parts.device)
     lse = torch.empty(lse_parts.shape[1:], dtype=torch.float32, device=o_parts.device) if return_lse else None
     with torch.cuda.device(o_parts.device):
-        _lib.check(lib.fa_merge_partials(o_parts.data_ptr(), lse_parts.data_ptr(), S, rows, D, out.data_ptr(),
-                                         _TORCH_TO_FA[out_dtype], lse.data_ptr() if lse is not None else None,
+        _lib.check(lib.fa_merge_partials(o_parts.data_ptr(), lse_parts.data_ptr(), S, rows, D, o_stride, l_stride,
+                                         out.data_ptr(), _TORCH_TO_FA[out_dtype], lse.data_ptr() if lse is not None else None,
                                          torch.cuda.current_stream(o_parts.device).cuda_stream), "fa_merge_partials")
     return (out, lse) if return_lse else out

@@ -61,8 +61,8 @@ def _declare(lib):
     lib.fa_decode_counters_len.restype = C.c_size_t
     lib.fa_decode_counters_len.argtypes = [C.c_int] * 4
     lib.fa_paged_decode_fwd.argtypes = [C.POINTER(DecodeArgs)]
-    lib.fa_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_int,
-                                      C.c_void_p, C.c_void_p]
+    lib.fa_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int64,
+                                      C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
     for name, argtypes in _OPTIONAL.items():
         if hasattr(lib, name):
             getattr(lib, name).argtypes = argtypes

@@ -168,11 +168,14 @@ FA_API int fa_paged_decode_fwd_static(const fa_decode_args* args);
  * Merge of normalised partial outputs over disjoint key ranges (the algebra of the reference merge
  * kernels, e.g. kernels/v8_gqa_ss/gqa_ss_attention.cu:209-231, with (m, l) folded into LSE).
  * Used after the all-gather of per-GPU partials when one sequence's keys are spread over GPUs.
- *   o_parts  : device float32 [n_parts, rows, D]     lse_parts : device float32 [n_parts, rows]
+ *   o_parts  : device float32, part s at o_parts + s * o_part_stride, each [rows, D]
+ *   lse_parts: device float32, part s at lse_parts + s * lse_part_stride, each [rows]
+ *              (strides in floats; <= 0 means densely packed [n_parts, rows, D] / [n_parts, rows])
  *   out      : device [rows, D] in out_dtype          lse_out   : optional float32 [rows]
  * ---------------------------------------------------------------------------------------------- */
 FA_API int fa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int64_t rows, int D,
-                      void* out, int out_dtype, float* lse_out, void* stream);
+                             int64_t o_part_stride, int64_t lse_part_stride, void* out, int out_dtype,
+                             float* lse_out, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * KV-cache formats and the paged layout (bit-exact with the reference's torch functions).

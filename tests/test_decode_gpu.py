@@ -288,3 +288,37 @@ def test_error_behaviour_matches_reference_contract():
         gqa_attention(q[..., :32].contiguous(), pool[..., :32].contiguous(), pool[..., :32].contiguous(), bt, 16, 64)
     with pytest.raises(RuntimeError, match="page_size"):
         gqa_attention(q, pool, pool, bt, 32, 64)
+
+
+# ------------------------------------------------------------- KV-range shards, emulated on one GPU
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("world", [2, 8])
+def test_kv_range_shards_merge_to_the_full_result(world, causal):
+    """What each rank of a KV-range-sharded decode computes (local pool slice, q_offset shifted by the
+    range start, output and LSE written into one flat send buffer) followed by the strided merge of
+    the gathered buffer — all ranks played in turn by one GPU, the all-gather replaced by a copy."""
+    from fa_kernels import gqa_attention
+    from fa_kernels._decode import merge_partials
+    from fa_kernels.distributed import kv_range_shards
+    B, H_kv, G, N_q, N_k, d, page = 2, 2, 4, 2, 3000, 128, 64
+    q_t, q = randn((B, G * H_kv, N_q, d), 61)
+    _, k = randn((B, H_kv, N_k, d), 611)
+    _, v = randn((B, H_kv, N_k, d), 612)
+    q_offset = N_k - N_q
+    rows, D = B * G * H_kv * N_q, d
+    recv = torch.empty(world, rows * (D + 1), dtype=torch.float32, device="cuda")
+    for r, (kb, ke) in enumerate(kv_range_shards(N_k, page, world)):
+        n = ke - kb
+        n_logical = max((n + page - 1) // page, 1)
+        perm = perm_for(B * n_logical, 61 + r)
+        kp, vp, bt, _ = O.build_paged_kv(np.ascontiguousarray(k[:, :, kb:ke]), np.ascontiguousarray(v[:, :, kb:ke]), page, perm) \
+            if n > 0 else (np.zeros((B, page, H_kv, d)), np.zeros((B, page, H_kv, d)), np.zeros((B, 1), np.int32), 0)
+        send = recv[r]
+        gqa_attention(q_t.cuda(), dev(kp, torch.float16), dev(vp, torch.float16), dev(bt), page, n, causal=causal,
+                      q_offset=q_offset - kb, out_dtype=torch.float32,
+                      out=send[: rows * D].view(B, G * H_kv, N_q, D), lse_out=send[rows * D:].view(B, G * H_kv, N_q))
+    out, lse = merge_partials(recv[:, : rows * D].unflatten(1, (B, G * H_kv, N_q, D)),
+                              recv[:, rows * D:].unflatten(1, (B, G * H_kv, N_q)), return_lse=True)
+    ref, ref_lse = O.gqa_attention_ref(q, k, v, causal=causal, q_offset=q_offset, return_lse=True)
+    assert_close(out, ref, what="kv-range merge")
+    np.testing.assert_allclose(lse.cpu().numpy(), ref_lse, atol=2e-3, rtol=1e-3)
