@@ -39,3 +39,47 @@ extern "C" int fa_device_sm_count(int* sm_count) {
   *sm_count = n;
   return FA_OK;
 }
+
+// ---- tensor maps -------------------------------------------------------------------------------------
+#include <cudaTypedefs.h>
+
+#include "sm100.cuh"
+
+namespace fa {
+
+int encode_tensor_map(CUtensorMap* out, int dtype, int rank, void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                      const uint32_t* box, int swizzle_128b) {
+  static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  if (encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr)
+      return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }
+  CUtensorMapDataType dt;
+  switch (dtype) {
+    case FA_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case FA_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case FA_E4M3: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case FA_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    default: return fail(FA_ERR_INVALID, "encode_tensor_map: unsupported dtype %d", dtype);
+  }
+  cuuint64_t gdim[5];
+  cuuint64_t gstr[5];
+  cuuint32_t bx[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    estr[i] = 1;
+    if (i + 1 < rank) gstr[i] = strides_bytes[i];
+  }
+  CUresult r = encode(out, dt, (cuuint32_t)rank, base, gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return FA_OK;
+}
+
+}  // namespace fa

@@ -32,3 +32,9 @@ def nvfp4_forward(q, k_pool, k_scale, v_pool, v_scale, block_table, page_size, n
     return _decode.paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal, q_offset,
                                 kv_format="nvfp4", k_micro=k_scale, v_micro=v_scale,
                                 scale_k=float(scale_k), scale_v=float(scale_v), **kw)
+
+
+def dense_forward(q, k, v, scale, causal, **kw):
+    """kernels/v1_naive/binding.cpp:7-14 (same signature in v2..v6)."""
+    from . import _dense
+    return _dense.dense_attention(q, k, v, scale, causal, **kw)

@@ -178,6 +178,31 @@ FA_API int fa_merge_partials(const float* o_parts, const float* lse_parts, int n
                              float* lse_out, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Dense attention forward (optionally causal) on tcgen05 tensor cores.
+ * Replaces `forward(q, k, v, scale, causal)` of kernels/v1_naive/binding.cpp:7-14 ... v6 (the call at
+ * fa_kernels/__init__.py:41-42).  q [B,H,N_q,D], k/v [B,H,N_k,D] contiguous, f16 or bf16, D in {64,128},
+ * 16-byte aligned.  causal masks key j when j > i (top-left aligned, kernels/v5_wmma/wmma_attention.cu:159).
+ * out [B,H,N_q,D] in out_dtype (FA_F32 = reference behaviour); lse optional float32 [B,H,N_q].
+ * status: optional device int; a non-zero value after the kernel names a pipeline wait that timed out
+ * (the kernel then ends early instead of hanging; the output is invalid).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fa_dense_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  int dtype;
+  int B, H, N_q, N_k, D;
+  float softmax_scale;
+  int causal;
+  void* out;
+  int out_dtype;
+  float* lse;
+  int* status;
+  void* stream;
+} fa_dense_args;
+FA_API int fa_dense_fwd(const fa_dense_args* args);
+
+/* ------------------------------------------------------------------------------------------------
  * KV-cache formats and the paged layout (bit-exact with the reference's torch functions).
  * ---------------------------------------------------------------------------------------------- */
 

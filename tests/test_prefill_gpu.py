@@ -1,0 +1,119 @@
+"""Parity of the dense tensor-core attention kernel with the oracle.
+
+Shape matrix of the reference's dense tests (tests/test_correctness.py:30-37, 110-141 there: six
+shapes incl. partial tiles N=130 / N=100, both mask modes, explicit scale) plus N_q != N_k, bf16, LSE,
+the CPU-plumbing configuration (B=2 H=8 N=512 d=64, seed 0, checked against the committed sample of
+the reference's own output) and the full-size fp16 causal prefill configuration on sampled heads."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close, randn
+from oracle import fa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 4, 128, 64), (2, 8, 512, 64), (1, 8, 512, 128), (1, 2, 2048, 64), (1, 2, 130, 64), (1, 2, 100, 128)]
+
+
+def _status_ok():
+    from fa_kernels._dense import status_word
+    torch.cuda.synchronize()
+    assert int(status_word(torch.device("cuda", torch.cuda.current_device())).item()) == 0, "a pipeline wait timed out"
+
+
+@pytest.mark.parametrize("B,H,N,d", SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+def test_matches_oracle(B, H, N, d, causal):
+    from fa_kernels import attention
+    q_t, q = randn((B, H, N, d), 0)
+    k_t, k = randn((B, H, N, d), 1)
+    v_t, v = randn((B, H, N, d), 2)
+    out, lse = attention(q_t.cuda(), k_t.cuda(), v_t.cuda(), causal=causal, backend="v5_wmma", return_lse=True)
+    _status_ok()
+    assert out.dtype == torch.float32
+    ref, ref_lse = O.attention_ref(q, k, v, causal=causal, return_lse=True)
+    assert_close(out, ref, what="dense")
+    np.testing.assert_allclose(lse.cpu().numpy(), ref_lse, atol=2e-3, rtol=1e-3)
+
+
+def test_explicit_scale_and_default_backend():
+    from fa_kernels import attention
+    q_t, q = randn((1, 4, 256, 64), 3)
+    k_t, k = randn((1, 4, 256, 64), 4)
+    v_t, v = randn((1, 4, 256, 64), 5)
+    out = attention(q_t.cuda(), k_t.cuda(), v_t.cuda(), scale=0.1)
+    _status_ok()
+    assert_close(out, O.attention_ref(q, k, v, scale=0.1), what="scale")
+
+
+@pytest.mark.parametrize("N_q,N_k,causal", [(1, 4096, False), (200, 1000, False), (1000, 200, True), (384, 384, True)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_rectangular_and_bf16(N_q, N_k, causal, dtype):
+    from fa_kernels import attention
+    q_t, q = randn((2, 3, N_q, 128), 6, dtype)
+    k_t, k = randn((2, 3, N_k, 128), 7, dtype)
+    v_t, v = randn((2, 3, N_k, 128), 8, dtype)
+    out = attention(q_t.cuda(), k_t.cuda(), v_t.cuda(), causal=causal, out_dtype=dtype)
+    _status_ok()
+    assert out.dtype == dtype
+    tol = dict(atol=2e-3, rtol=1e-2) if dtype == torch.float16 else dict(atol=8e-3, rtol=2e-2)
+    assert_close(out, O.attention_ref(q, k, v, causal=causal), what="rect", **tol)
+
+
+def test_long_sequence_rescale_stability():
+    from fa_kernels import attention
+    q_t, q = randn((1, 1, 16384, 64), 9)
+    k_t, k = randn((1, 1, 16384, 64), 10)
+    v_t, v = randn((1, 1, 16384, 64), 11)
+    q_t, q = q_t * 3, q * 3                      # sharper softmax: the running max keeps moving
+    out = attention(q_t.cuda(), k_t.cuda(), v_t.cuda(), causal=True)
+    _status_ok()
+    rows = slice(16000, 16384)
+    ref = O.attention_ref(q[:, :, rows], k, v, causal=True, q_offset=16000)
+    assert_close(out[:, :, rows], ref, what="long")
+
+
+def test_config1_cpu_plumbing_case_against_reference_sample(golden):
+    """Dense causal MHA B=2 H=8 N=512 d=64 from seed 0, scale 0.125; fp32 inputs are cast to half on
+    entry like the reference's tensor-core backend, so the comparison with the reference's fp32 output
+    sample uses that backend's 2e-2 band, and the oracle on the rounded inputs the tight one."""
+    from fa_kernels import attention
+    g = golden("config1_sample.npz")
+    torch.manual_seed(0)
+    q = torch.randn(2, 8, 512, 64)
+    k = torch.randn(2, 8, 512, 64)
+    v = torch.randn(2, 8, 512, 64)
+    stride = int(g["stride"])
+    np.testing.assert_array_equal(q.flatten()[::stride].numpy(), g["q_sample"])
+    out, lse = attention(q.cuda(), k.cuda(), v.cuda(), causal=True, scale=0.125, return_lse=True)
+    _status_ok()
+    got = out.cpu().numpy()
+    assert np.abs(got.reshape(-1)[::stride] - g["out_sample"]).max() < 2e-2
+    qh, kh, vh = (x.half().float().numpy().astype(np.float64) for x in (q, k, v))
+    ref, ref_lse = O.attention_ref(qh, kh, vh, causal=True, scale=0.125, return_lse=True)
+    assert_close(out, ref, what="config 1")
+    np.testing.assert_allclose(lse.cpu().numpy(), ref_lse, atol=2e-3, rtol=1e-3)
+
+
+def test_full_size_causal_prefill_sampled_heads():
+    """B=4 H=32 N=4096 d=128 fp16, q/k/v ~ N(0,1)*0.5 from seed 1; every head is computed, six are
+    compared with the oracle, and all heads must be finite with rows that are convex combinations of V."""
+    from fa_kernels import attention
+    g = torch.Generator(device="cuda").manual_seed(1)
+    shape = (4, 32, 4096, 128)
+    q = (torch.randn(shape, device="cuda", generator=g) * 0.5).half()
+    k = (torch.randn(shape, device="cuda", generator=g) * 0.5).half()
+    v = (torch.randn(shape, device="cuda", generator=g) * 0.5).half()
+    out = attention(q, k, v, causal=True, out_dtype=torch.float16)
+    _status_ok()
+    assert torch.isfinite(out).all()
+    assert (out.float().abs().amax(dim=(2, 3)) <= v.float().abs().amax(dim=(2, 3)) + 1e-3).all()
+    assert torch.equal(out[:, :, 0], v[:, :, 0])          # the first causal row sees only key 0
+    for b, h in [(0, 0), (0, 31), (1, 7), (2, 16), (3, 0), (3, 31)]:
+        ref = O.attention_ref(q[b:b + 1, h:h + 1].float().cpu().numpy(), k[b:b + 1, h:h + 1].float().cpu().numpy(),
+                              v[b:b + 1, h:h + 1].float().cpu().numpy(), causal=True)
+        assert_close(out[b:b + 1, h:h + 1], ref, what=f"config 2 head {b},{h}")
