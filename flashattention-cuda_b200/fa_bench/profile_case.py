@@ -26,6 +26,11 @@ def make_step(name, device, batch=None):
         fn = lambda: gqa_attention(w["q"], w["k_pool"], w["v_pool"], w["block_table"], w["page_size"], w["seq_lens"],
                                    out_dtype=torch.float16)
         return fn, w["kv_bytes"]
+    if name == "causal_prefill_fp16":
+        from fa_kernels import attention
+        w = workloads.causal_prefill(device, batch=batch or 4)
+        fn = lambda: attention(w["q"], w["k"], w["v"], causal=True, out_dtype=torch.float16)
+        return fn, w["flops"]
     raise SystemExit(f"unknown workload {name!r}")
 
 
@@ -39,7 +44,8 @@ def main():
     dev = torch.device("cuda:0")
     fn, nbytes = make_step(args.workload, dev, args.batch)
     for i, ms in enumerate(timing.time_cuda(fn, warmup=1, iters=args.launches - 1, device=dev)):
-        print(f"launch {i + 1}: {ms * 1e3:.1f} us  {nbytes / ms / 1e6:.0f} GB/s")
+        unit = "GFLOP/s" if "prefill" in args.workload or "mla" in args.workload else "GB/s"
+        print(f"launch {i + 1}: {ms * 1e3:.1f} us  {nbytes / ms / 1e6:.0f} {unit}")
 
 
 if __name__ == "__main__":

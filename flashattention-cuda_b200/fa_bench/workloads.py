@@ -40,3 +40,13 @@ def paged_gqa_decode(device, *, batch=64, h_q=32, h_kv=8, d=128, page_size=16, m
     return dict(q=q, k_pool=k_pool, v_pool=v_pool, block_table=bt.to(device), block_table_host=bt,
                 page_size=page_size, seq_lens=seq_lens, tokens=tokens, kv_bytes=kv_bytes,
                 total_bytes=kv_bytes + other, flops=4 * h_q * d * tokens)
+
+
+def causal_prefill(device, *, batch=4, heads=32, n=4096, d=128, seed=1, dtype=torch.float16):
+    """Dense causal prefill: q, k, v ~ N(0,1) * 0.5 from `seed`, [batch, heads, n, d]."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    shape = (batch, heads, n, d)
+    q, k, v = ((torch.randn(shape, device=device, generator=g) * 0.5).to(dtype) for _ in range(3))
+    flops_causal = 2 * batch * heads * d * n * (n + 1)          # both matmuls, lower triangle only
+    return dict(q=q, k=k, v=v, flops=flops_causal, flops_full=4 * batch * heads * n * n * d,
+                bytes=4 * q.numel() * q.element_size())
