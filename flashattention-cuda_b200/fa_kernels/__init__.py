@@ -11,10 +11,11 @@ and a missing library or GPU is an error, never a fallback.
 from __future__ import annotations
 
 from .config import AttnConfig
-from .paged import build_paged_kv_mla, fp8_attention, gqa_attention, nvfp4_attention, paged_attention
+from .paged import (build_paged_kv_mla, fp8_attention, gqa_attention, mla_attention, mla_tc_attention,
+                    nvfp4_attention, paged_attention)
 
 __all__ = ["attention", "paged_attention", "gqa_attention", "fp8_attention", "nvfp4_attention",
-           "build_paged_kv_mla", "AttnConfig"]
+           "mla_attention", "mla_tc_attention", "build_paged_kv_mla", "AttnConfig"]
 
 # The reference's default is its teaching baseline "v1_naive" (fa_kernels/__init__.py:23); every dense
 # backend name maps to the one tensor-core kernel here.

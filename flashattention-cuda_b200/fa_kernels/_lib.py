@@ -70,6 +70,7 @@ def _declare(lib):
 
 # entry points declared by later sections of include/fa_b200.h (argtypes filled in when present)
 _OPTIONAL: dict = {
+    "fa_mla_decode_fwd": [C.c_void_p],
     "fa_dense_fwd": [C.c_void_p],
     "fa_paged_decode_fwd_static": [C.POINTER(DecodeArgs)],
     "fa_quantize_fp8_e4m3": [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p],

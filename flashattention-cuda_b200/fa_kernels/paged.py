@@ -74,6 +74,35 @@ def nvfp4_attention(q, k_pack, k_micro, v_pack, v_micro, block_table, page_size,
                           float(scale_k), float(scale_v), _default_scale(q, scale), causal, q_offset, **kw)
 
 
+def mla_attention(q, l_pack, l_micro, block_table, page_size, n_k, kv_lora_rank, scale_l, *, scale=None,
+                  causal=False, q_offset=0, backend=DEFAULT_MLA_BACKEND, **kw):
+    """MLA latent-KV decode (reference fa_kernels/paged.py:312-340): all H_q heads attend one shared
+    latent; scores over DQK, output = p-weighted sum of the first `kv_lora_rank` latent dims,
+    [B, H_q, N_q, kv_lora_rank].  Default scale 1/sqrt(DQK).  `l_pack` is the packed NVFP4 pool of
+    `build_paged_kv_mla` with `l_micro` its micro-scales, or a bf16 / FP8 E4M3 latent pool
+    [num_blocks, page_size, 1, DQK] (then `l_micro` is ignored and `scale_l` is a float or, for FP8,
+    per-token float32 scales [num_blocks, page_size, 1])."""
+    from .dispatch import get_backend
+    module = get_backend(backend)
+    return module.forward(q, l_pack, l_micro, block_table, int(page_size), n_k, int(kv_lora_rank), scale_l,
+                          _default_scale(q, scale), causal, q_offset, **kw)
+
+
+_MLA_TC_ENGINES = {"fp8": 0, "nvfp4": 1}
+
+
+def mla_tc_attention(q, l_pack, l_micro, block_table, page_size, n_k, kv_lora_rank, scale_l, *, engine="fp8",
+                     scale=None, causal=False, q_offset=0, backend=DEFAULT_MLA_TC_BACKEND, **kw):
+    """Tensor-core MLA decode (reference fa_kernels/paged.py:346-376): same inputs and output as
+    `mla_attention`; `engine` in {"fp8", "nvfp4"} is validated as in the reference."""
+    from .dispatch import get_backend
+    if engine not in _MLA_TC_ENGINES:
+        raise ValueError(f"engine must be one of {sorted(_MLA_TC_ENGINES)}; got {engine!r}")
+    module = get_backend(backend)
+    return module.forward(q, l_pack, l_micro, block_table, int(page_size), n_k, int(kv_lora_rank), scale_l,
+                          _default_scale(q, scale), causal, q_offset, int(_MLA_TC_ENGINES[engine]), **kw)
+
+
 # ---- layout builders and quantisers (reference fa_kernels/paged.py:48-212, 287-309) ------------------
 # Thin lazy forwards so that `import fa_kernels` needs neither torch nor the CUDA library.
 def _fwd(name):

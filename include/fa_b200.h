@@ -203,6 +203,54 @@ typedef struct fa_dense_args {
 FA_API int fa_dense_fwd(const fa_dense_args* args);
 
 /* ------------------------------------------------------------------------------------------------
+ * MLA latent-KV decode: MQA of H_q heads over one shared latent per token; scores over DQK dims, values
+ * = the first DV dims of the same latent.  Replaces `forward` of kernels/v11_mla/binding.cpp and
+ * kernels/v12_mla_tc/binding.cpp:11-27 (the calls at fa_kernels/paged.py:338-340, 373-376).
+ *   q       : device [B, H_q, N_q, DQK], FA_BF16 with a bf16 latent, FA_F16 otherwise
+ *   l_pool  : device [num_blocks, page_size, 1, DX]: bf16 (DX = DQK), uint8 E4M3 (DX = DQK) or packed
+ *             NVFP4 nibbles (DX = DQK/2, with l_micro [.., 1, DQK/16] E4M3 micro-scales — the reference
+ *             layout of build_paged_kv_mla, paged.py:287-309)
+ *   l_scale : per-tensor scale (`scale_l`); l_token_scale: optional float32 [num_blocks, page_size, 1]
+ *             per-token scales of an E4M3 latent (multiply l_scale)
+ *   (DQK, DV) in {(576,512), (160,128), (96,64)} as in kernels/v11_mla/mla_attention.cu:383-397.
+ * Plan, workspace and counters as for fa_paged_decode_fwd, with H_kv = 1 and 32-row tiles: call
+ * fa_decode_plan(..., H_kv = 1, rows = 16 * ceil(H_q * N_q / 32), ...), workspace bytes =
+ * fa_decode_workspace_bytes(n_slots, H_q, N_q, DV), counters = fa_mla_counters_len(B, H_q, N_q).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct fa_mla_args {
+  const void* q;
+  int q_dtype;
+  const void* l_pool;
+  int latent_dtype;
+  const void* l_micro;
+  float l_scale;
+  const float* l_token_scale;
+  const int32_t* block_table;
+  int n_logical;
+  int num_blocks;
+  int page_size;
+  int B, H_q, N_q, DQK, DV;
+  float softmax_scale;
+  int causal;
+  int q_offset;
+  const int32_t* q_offsets;
+  const fa_decode_item* items;
+  int n_items;
+  int n_slots;
+  int max_range_keys;
+  void* out;
+  int out_dtype;
+  float* lse;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* counters;
+  size_t counters_len;
+  void* stream;
+} fa_mla_args;
+FA_API size_t fa_mla_counters_len(int B, int H_q, int N_q);
+FA_API int fa_mla_decode_fwd(const fa_mla_args* args);
+
+/* ------------------------------------------------------------------------------------------------
  * KV-cache formats and the paged layout (bit-exact with the reference's torch functions).
  * ---------------------------------------------------------------------------------------------- */
 
