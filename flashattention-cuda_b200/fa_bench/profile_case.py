@@ -31,6 +31,12 @@ def make_step(name, device, batch=None):
         w = workloads.causal_prefill(device, batch=batch or 4)
         fn = lambda: attention(w["q"], w["k"], w["v"], causal=True, out_dtype=torch.float16)
         return fn, w["flops"]
+    if name in ("mla_decode_bf16", "mla_decode_fp8"):
+        from fa_kernels import mla_attention
+        w = workloads.mla_decode(device, batch=batch or 128, latent="bf16" if name.endswith("bf16") else "e4m3")
+        fn = lambda: mla_attention(w["q"], w["l_pool"], None, w["block_table"], w["page_size"], w["seq_lens"],
+                                   w["kv_lora_rank"], w["scale_l"], out_dtype=torch.bfloat16 if name.endswith("bf16") else torch.float16)
+        return fn, w["flops"]
     raise SystemExit(f"unknown workload {name!r}")
 
 

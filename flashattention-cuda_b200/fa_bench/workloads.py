@@ -50,3 +50,41 @@ def causal_prefill(device, *, batch=4, heads=32, n=4096, d=128, seed=1, dtype=to
     flops_causal = 2 * batch * heads * d * n * (n + 1)          # both matmuls, lower triangle only
     return dict(q=q, k=k, v=v, flops=flops_causal, flops_full=4 * batch * heads * n * n * d,
                 bytes=4 * q.numel() * q.element_size())
+
+
+def mla_decode(device, *, batch=128, h_q=128, dqk=576, dv=512, page_size=64, min_len=4096, max_len=32768, seed=5,
+               latent="bf16", seq_lens=None):
+    """MLA latent decode (DeepSeek-V3-like): q ~ N(0,1), latent ~ N(0,1) * 0.1 drawn straight into the
+    paged pool, context lengths uniform in [min_len, max_len]; latent stored as bf16 or as E4M3 bytes
+    with one fp32 scale per token (scale = amax / 448)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    if seq_lens is None:
+        seq_lens = torch.randint(min_len, max_len + 1, (batch,), generator=g).tolist()
+    batch = len(seq_lens)
+    n_pages = [(n + page_size - 1) // page_size for n in seq_lens]
+    total_pages = sum(n_pages)
+    perm = torch.randperm(total_pages, generator=g)
+    bt = torch.zeros(batch, max(n_pages), dtype=torch.int32)
+    cur = 0
+    for b, np_ in enumerate(n_pages):
+        bt[b, :np_] = perm[cur:cur + np_].to(torch.int32)
+        cur += np_
+    gd = torch.Generator(device=device).manual_seed(seed)
+    pool = torch.empty(total_pages, page_size, 1, dqk, device=device, dtype=torch.bfloat16)
+    step = 4096
+    for i in range(0, total_pages, step):                      # generate in slabs to bound fp32 temporaries
+        n = min(step, total_pages - i)
+        pool[i:i + n] = (torch.randn(n, page_size, 1, dqk, device=device, generator=gd) * 0.1).to(torch.bfloat16)
+    q = torch.randn(batch, h_q, 1, dqk, device=device, generator=gd)
+    tokens = sum(seq_lens)
+    out = dict(block_table=bt.to(device), block_table_host=bt, page_size=page_size, seq_lens=seq_lens, tokens=tokens,
+               kv_lora_rank=dv, flops=2 * h_q * (dqk + dv) * tokens)
+    if latent == "bf16":
+        out.update(q=q.to(torch.bfloat16), l_pool=pool, scale_l=1.0, latent_bytes=tokens * dqk * 2)
+    elif latent == "e4m3":
+        from fa_kernels.paged import quantize_fp8_e4m3_per_token
+        bytes_, scales = quantize_fp8_e4m3_per_token(pool)
+        out.update(q=q.to(torch.float16), l_pool=bytes_, scale_l=scales, latent_bytes=tokens * (dqk + 4))
+    else:
+        raise ValueError(latent)
+    return out
