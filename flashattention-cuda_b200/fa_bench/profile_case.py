@@ -18,7 +18,7 @@ sys.path.insert(0, os.path.dirname(HERE))
 import torch  # noqa: E402
 
 
-def make_step(name, device, batch=None):
+def make_step(name, device, batch=None, ctx=None):
     from fa_bench import workloads
     from fa_kernels import gqa_attention
     if name == "paged_gqa_decode_fp16":
@@ -37,6 +37,17 @@ def make_step(name, device, batch=None):
         fn = lambda: mla_attention(w["q"], w["l_pool"], None, w["block_table"], w["page_size"], w["seq_lens"],
                                    w["kv_lora_rank"], w["scale_l"], out_dtype=torch.bfloat16 if name.endswith("bf16") else torch.float16)
         return fn, w["flops"]
+    if name in ("long_decode_fp8", "long_decode_nvfp4"):
+        from fa_kernels import fp8_attention, nvfp4_attention
+        w = workloads.quantised_long_context_decode(device, fmt="e4m3" if name.endswith("fp8") else "nvfp4",
+                                                    batch=batch or 4, ctx=ctx or 1048576)
+        if name.endswith("fp8"):
+            fn = lambda: fp8_attention(w["q"], w["k_pool"], w["v_pool"], w["block_table"], w["page_size"], w["n_k"],
+                                       w["k_scale"], w["v_scale"], out_dtype=torch.float16)
+        else:
+            fn = lambda: nvfp4_attention(w["q"], w["k_pool"], w["k_micro"], w["v_pool"], w["v_micro"], w["block_table"],
+                                         w["page_size"], w["n_k"], w["k_scale"], w["v_scale"], out_dtype=torch.float16)
+        return fn, w["kv_bytes"]
     raise SystemExit(f"unknown workload {name!r}")
 
 
@@ -45,10 +56,11 @@ def main():
     ap.add_argument("--workload", default="paged_gqa_decode_fp16")
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--ctx", type=int, default=None, help="context length of the long-context workloads")
     args = ap.parse_args()
     from fa_bench import timing
     dev = torch.device("cuda:0")
-    fn, nbytes = make_step(args.workload, dev, args.batch)
+    fn, nbytes = make_step(args.workload, dev, args.batch, args.ctx)
     for i, ms in enumerate(timing.time_cuda(fn, warmup=1, iters=args.launches - 1, device=dev)):
         unit = "GFLOP/s" if "prefill" in args.workload or "mla" in args.workload else "GB/s"
         print(f"launch {i + 1}: {ms * 1e3:.1f} us  {nbytes / ms / 1e6:.0f} {unit}")

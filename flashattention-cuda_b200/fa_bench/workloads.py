@@ -88,3 +88,36 @@ def mla_decode(device, *, batch=128, h_q=128, dqk=576, dv=512, page_size=64, min
     else:
         raise ValueError(latent)
     return out
+
+
+def quantised_long_context_decode(device, *, fmt="e4m3", batch=4, h_q=32, h_kv=8, d=128, ctx=1048576, page_size=64, seed=3):
+    """Quantised-KV long-context GQA decode: K, V ~ N(0,1) with a fixed random 1 % of the channels
+    (per KV head) scaled x10, quantised (a) "e4m3": FP8 with one fp32 scale per token per head =
+    amax / 448, or (b) "nvfp4": E2M1 + one E4M3 scale per 16 elements + one fp32 tensor scale; paged
+    with a shuffled block table.  Built sequence by sequence to bound the fp32 temporaries."""
+    from fa_kernels import paged as P
+    gd = torch.Generator(device=device).manual_seed(seed)
+    n_out = max(1, round(0.01 * d))
+    chan = torch.ones(1, h_kv, 1, d, device=device)
+    for h in range(h_kv):
+        idx = torch.randperm(d, device=device, generator=gd)[:n_out]
+        chan[0, h, 0, idx] = 10.0
+    k = torch.empty(batch, h_kv, ctx, d, device=device, dtype=torch.float16)
+    v = torch.empty(batch, h_kv, ctx, d, device=device, dtype=torch.float16)
+    for b in range(batch):
+        k[b] = (torch.randn(1, h_kv, ctx, d, device=device, generator=gd) * chan)[0].half()
+        v[b] = (torch.randn(1, h_kv, ctx, d, device=device, generator=gd) * chan)[0].half()
+    q = torch.randn(batch, h_q, 1, d, device=device, generator=gd).half()
+    tokens = batch * ctx
+    w = dict(q=q, page_size=page_size, n_k=ctx, tokens=tokens, fmt=fmt, flops=4 * h_q * d * tokens)
+    if fmt == "e4m3":
+        kp, vp, bt, _, ks, vs = P.build_paged_kv_fp8_per_token(k, v, page_size, seed=seed)
+        w.update(k_pool=kp, v_pool=vp, block_table=bt, k_scale=ks, v_scale=vs, kv_bytes=2 * h_kv * tokens * (d + 4))
+    elif fmt == "nvfp4":
+        kp, km, vp, vm, bt, _, sk, sv = P.build_paged_kv_nvfp4(k, v, page_size, seed=seed)
+        w.update(k_pool=kp, k_micro=km, v_pool=vp, v_micro=vm, block_table=bt, k_scale=sk, v_scale=sv,
+                 kv_bytes=2 * h_kv * tokens * (d // 2 + d // 16))
+    else:
+        raise ValueError(fmt)
+    del k, v
+    return w
