@@ -84,6 +84,32 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
   }
 }
 
+// Same product when only rows 0..7 of the 16-row tile are real: the A registers of rows 8..15 and their
+// accumulators are zero on input and the results for those rows are dropped.
+template <bool BF16, bool R8>
+__device__ __forceinline__ void mma_rows(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (!R8) {
+    mma16816<BF16>(c, a, b0, b1);
+  } else {
+    float d2, d3;
+    const uint32_t z = 0u;
+    const float zf = 0.f;
+    if constexpr (BF16) {
+      asm volatile(
+          "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+          "{%10,%11,%12,%13};\n"
+          : "=f"(c[0]), "=f"(c[1]), "=f"(d2), "=f"(d3)
+          : "r"(a[0]), "r"(z), "r"(a[2]), "r"(z), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(zf), "f"(zf));
+    } else {
+      asm volatile(
+          "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+          "{%10,%11,%12,%13};\n"
+          : "=f"(c[0]), "=f"(c[1]), "=f"(d2), "=f"(d3)
+          : "r"(a[0]), "r"(z), "r"(a[2]), "r"(z), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(zf), "f"(zf));
+    }
+  }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));

@@ -94,8 +94,12 @@ __device__ __forceinline__ int q_dim(int ks, int c, int sel) {
   else return 16 * ks + 2 * c + 8 * sel;
 }
 
-template <int D, int FMT, int NSTAGE, int MINB>
+template <int D, int FMT, int NSTAGE, int MINB, bool R8>
 __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const DecodeParams p) {
+  // R8: at most 8 packed query rows (decode with G <= 8): rows 8..15 of the 16-row MMA tile are padding,
+  // their A-fragment registers are constant zero and their accumulators are never kept, which halves
+  // the register footprint of S and O.
+  constexpr int NR = R8 ? 1 : 2;
   using G_ = Geo<D, FMT>;
   constexpr int KROW = G_::KROW;
   constexpr int CPR = G_::CPR;
@@ -126,10 +130,10 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
 
   // ---- per-row limits (largest key index a row may attend) -------------------------------------
   const int rows_valid = min(kRowTile, p.M - m0);
-  int lim[2];
+  int lim[2] = {INT_MAX, INT_MAX};
   int tile_max_lim = p.causal ? INT_MIN : INT_MAX, tile_min_lim = INT_MAX;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < NR; ++r) {
     const int row = g4 + 8 * r;
     lim[r] = INT_MAX;
     if (p.causal && row < rows_valid) {
@@ -168,10 +172,10 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
   }
 
   // ---- query fragments (registers, whole kernel) -----------------------------------------------
-  uint32_t qf[NKS][4];
+  uint32_t qf[NKS][4] = {};
   {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NR; ++r) {
       const int row = g4 + 8 * r;
       const int m = m0 + row;
       const bool ok = row < rows_valid;
@@ -292,18 +296,18 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
         for (int ks = 0; ks < NKS; ++ks) {
           uint32_t r[4];
           ldmatrix_x4(r, kbase + swz<KROW>(krow, 2 * ks + csel) * 16);
-          mma16816<BF>(s[0], qf[ks], r[0], r[1]);
-          mma16816<BF>(s[1], qf[ks], r[2], r[3]);
+          mma_rows<BF, R8>(s[0], qf[ks], r[0], r[1]);
+          mma_rows<BF, R8>(s[1], qf[ks], r[2], r[3]);
         }
       } else if constexpr (FMT == KV_E4M3) {
 #pragma unroll
         for (int kp = 0; kp < NKS / 2; ++kp) {
           uint32_t r[4];
           ldmatrix_x4(r, kbase + swz<KROW>(krow, 2 * kp + csel) * 16);
-          mma16816<false>(s[0], qf[2 * kp], e4m3x2_to_h2(r[0]), e4m3x2_to_h2(r[0] >> 16));
-          mma16816<false>(s[0], qf[2 * kp + 1], e4m3x2_to_h2(r[1]), e4m3x2_to_h2(r[1] >> 16));
-          mma16816<false>(s[1], qf[2 * kp], e4m3x2_to_h2(r[2]), e4m3x2_to_h2(r[2] >> 16));
-          mma16816<false>(s[1], qf[2 * kp + 1], e4m3x2_to_h2(r[3]), e4m3x2_to_h2(r[3] >> 16));
+          mma_rows<false, R8>(s[0], qf[2 * kp], e4m3x2_to_h2(r[0]), e4m3x2_to_h2(r[0] >> 16));
+          mma_rows<false, R8>(s[0], qf[2 * kp + 1], e4m3x2_to_h2(r[1]), e4m3x2_to_h2(r[1] >> 16));
+          mma_rows<false, R8>(s[1], qf[2 * kp], e4m3x2_to_h2(r[2]), e4m3x2_to_h2(r[2] >> 16));
+          mma_rows<false, R8>(s[1], qf[2 * kp + 1], e4m3x2_to_h2(r[3]), e4m3x2_to_h2(r[3] >> 16));
         }
       } else {
         // NVFP4: one 16-byte chunk = 32 head dims = 2 k-steps; lane-in-quad c owns dims 8c..8c+7 of
@@ -333,8 +337,8 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
             e2m1x8_to_h2x4(r[j], h);
             const uint32_t mb = (mic[n] >> (8 * ch)) & 0xffu;
             const uint32_t mh = e4m3x2_to_h2(mb | (mb << 8));
-            mma16816<false>(s[n], qf[2 * ch], hmul2_u32(h[0], mh), hmul2_u32(h[1], mh));
-            mma16816<false>(s[n], qf[2 * ch + 1], hmul2_u32(h[2], mh), hmul2_u32(h[3], mh));
+            mma_rows<false, R8>(s[n], qf[2 * ch], hmul2_u32(h[0], mh), hmul2_u32(h[1], mh));
+            mma_rows<false, R8>(s[n], qf[2 * ch + 1], hmul2_u32(h[2], mh), hmul2_u32(h[3], mh));
           }
         }
       }
@@ -365,13 +369,13 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int key = kt + kw + 8 * n + 2 * c + (e & 1);
-          if (key > lim[e >> 1]) s[n][e] = -INFINITY;
+          if ((!R8 || e < 2) && key > lim[e >> 1]) s[n][e] = -INFINITY;
         }
     }
-    float alpha[2];
+    float alpha[2] = {1.f, 1.f};
     bool changed = false;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NR; ++r) {
       float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -393,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
 #pragma unroll
       for (int tt = 0; tt < NOT; ++tt) {
         o[tt][0] *= alpha[0]; o[tt][1] *= alpha[0];
-        o[tt][2] *= alpha[1]; o[tt][3] *= alpha[1];
+        if constexpr (!R8) { o[tt][2] *= alpha[1]; o[tt][3] *= alpha[1]; }
       }
     }
 
@@ -417,8 +421,8 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
         for (int jp = 0; jp < D / 16; ++jp) {
           uint32_t r[4];
           ldmatrix_x4_trans(r, vbase + swz<KROW>(vrow, 2 * jp + csel) * 16);
-          mma16816<BF>(o[2 * jp], pa, r[0], r[1]);
-          mma16816<BF>(o[2 * jp + 1], pa, r[2], r[3]);
+          mma_rows<BF, R8>(o[2 * jp], pa, r[0], r[1]);
+          mma_rows<BF, R8>(o[2 * jp + 1], pa, r[2], r[3]);
         }
       } else if constexpr (FMT == KV_E4M3) {
         // after the 16-bit transpose a register holds (k0,d0)(k0,d1)(k1,d0)(k1,d1); regroup to
@@ -432,8 +436,8 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
             const uint32_t x0 = prmt(r[2 * u], 0u, 0x3120u);
             const uint32_t x1 = prmt(r[2 * u + 1], 0u, 0x3120u);
             const int j = 2 * jp + u;
-            mma16816<false>(o[2 * j], pa, e4m3x2_to_h2(x0), e4m3x2_to_h2(x1));
-            mma16816<false>(o[2 * j + 1], pa, e4m3x2_to_h2(x0 >> 16), e4m3x2_to_h2(x1 >> 16));
+            mma_rows<false, R8>(o[2 * j], pa, e4m3x2_to_h2(x0), e4m3x2_to_h2(x1));
+            mma_rows<false, R8>(o[2 * j + 1], pa, e4m3x2_to_h2(x0 >> 16), e4m3x2_to_h2(x1 >> 16));
           }
         }
       } else {
@@ -482,7 +486,7 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
               bfrag[u][3] = hmul2_u32(prmt(h[1], h[3], 0x7632u), mm);
             }
 #pragma unroll
-            for (int qd = 0; qd < 4; ++qd) mma16816<false>(o[4 * ch + qd], pa, bfrag[0][qd], bfrag[1][qd]);
+            for (int qd = 0; qd < 4; ++qd) mma_rows<false, R8>(o[4 * ch + qd], pa, bfrag[0][qd], bfrag[1][qd]);
           }
         }
       }
@@ -496,14 +500,14 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
   float* s_m = s_o + kWarps * kRowTile * D;                    // [warp][16]
   float* s_l = s_m + kWarps * kRowTile;                        // [warp][16]
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < NR; ++r) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
   }
   {
     const float out_scale = p.v_scale;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NR; ++r) {
       const int row = g4 + 8 * r;
       if (row < rows_valid) {
         float* dst = s_o + (warp * kRowTile + row) * D;
@@ -588,13 +592,13 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
   }
 }
 
-template <int D, int FMT, int NSTAGE, int MINB>
+template <int D, int FMT, int NSTAGE, int MINB, bool R8>
 int launch_decode(const DecodeParams& p, int n_items, int row_tiles, cudaStream_t stream) {
   using G_ = Geo<D, FMT>;
   constexpr int PIPE = (NSTAGE * G_::STAGE > G_::MERGE) ? NSTAGE * G_::STAGE : G_::MERGE;
   const int SMEM = PIPE + p.bt_cap * 4;
   constexpr int SMEM_MAX = PIPE + kMaxPages * 4;
-  auto kern = paged_decode_kernel<D, FMT, NSTAGE, MINB>;
+  auto kern = paged_decode_kernel<D, FMT, NSTAGE, MINB, R8>;
   static int configured_device = -1;   // attribute is per device
   int dev = 0;
   FA_CUDA_OK(cudaGetDevice(&dev));
@@ -653,22 +657,25 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     FA_CHECK_ARG(len >= 0, "fa_decode_plan: negative sequence length at b=%d", b);
     total += len;
   }
-  // Every range pays a fixed start-up (metadata, block table, pipeline fill), so sequences are cut only
-  // when there are fewer (sequence, head, row tile) units than CTA slots (2 per SM); then ~2 ranges
-  // per slot, never shorter than 256 keys.
+  // Every range pays a fixed start-up (metadata, block table, pipeline fill; worth ~300 keys), so
+  // sequences are cut only when there are fewer (sequence, head, row tile) units than CTA slots (up to
+  // 3 per SM): into ~8 waves of ranges when those stay >= 2048 keys, else ~2 ranges per slot, never
+  // shorter than 256 keys.
   const int64_t max_chunk = (int64_t)(kMaxPages - 1) * page_size / kTN * kTN;
   FA_CHECK_ARG(max_chunk >= kTN, "fa_decode_plan: page_size too small");
   int64_t chunk;
   if (chunk_hint > 0) {
     chunk = chunk_hint;
   } else {
-    const int64_t slots = (int64_t)num_sms * 2;
+    const int64_t slots = (int64_t)num_sms * 3;
     const int64_t units = (int64_t)B * H_kv * row_tiles;
+    const int64_t work = total * H_kv * row_tiles;      // keys x heads x row tiles
     if (units >= slots) {
       chunk = max_chunk;
+    } else if (work / (8 * slots) >= 2048) {
+      chunk = work / (8 * slots);                       // long contexts: ~8 waves of ranges, start-up stays < 10 %
     } else {
-      chunk = (total * H_kv * row_tiles + 2 * slots - 1) / (2 * slots);
-      chunk = std::max<int64_t>(chunk, 256);
+      chunk = std::max<int64_t>((work + 2 * slots - 1) / (2 * slots), 256);
     }
   }
   chunk = (chunk + kTN - 1) / kTN * kTN;
@@ -788,20 +795,30 @@ extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
   p.n_items = a->n_items; p.head_major = (a->variant == 2);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
 
-#define FA_LAUNCH(D_, F_, NS_, MB_) return launch_decode<D_, F_, NS_, MB_>(p, a->n_items, row_tiles, st)
+#define FA_LAUNCH(D_, F_, NS_, MB_, R8_) return launch_decode<D_, F_, NS_, MB_, R8_>(p, a->n_items, row_tiles, st)
+  // R8 kernels: at most 8 packed rows (decode with G <= 8), rows 8..15 of the MMA tile are never kept.
+  const bool r8 = (M <= 8);
   if (a->D == 128) {
     switch (fmt) {
-      case KV_F16: if (a->variant == 1) FA_LAUNCH(128, KV_F16, 4, 1); FA_LAUNCH(128, KV_F16, 3, 2);
-      case KV_BF16: FA_LAUNCH(128, KV_BF16, 3, 2);
-      case KV_E4M3: if (a->variant == 1) FA_LAUNCH(128, KV_E4M3, 6, 2); FA_LAUNCH(128, KV_E4M3, 4, 3);
-      default: if (a->variant == 1) FA_LAUNCH(128, KV_NVFP4, 8, 2); FA_LAUNCH(128, KV_NVFP4, 6, 3);
+      case KV_F16:
+        if (r8) { if (a->variant == 1) FA_LAUNCH(128, KV_F16, 2, 3, true); FA_LAUNCH(128, KV_F16, 3, 2, true); }
+        FA_LAUNCH(128, KV_F16, 3, 2, false);
+      case KV_BF16:
+        if (r8) FA_LAUNCH(128, KV_BF16, 3, 2, true);
+        FA_LAUNCH(128, KV_BF16, 3, 2, false);
+      case KV_E4M3:
+        if (r8) FA_LAUNCH(128, KV_E4M3, 4, 3, true);
+        FA_LAUNCH(128, KV_E4M3, 4, 3, false);
+      default:
+        if (r8) FA_LAUNCH(128, KV_NVFP4, 6, 3, true);
+        FA_LAUNCH(128, KV_NVFP4, 6, 3, false);
     }
   } else {
     switch (fmt) {
-      case KV_F16: FA_LAUNCH(64, KV_F16, 4, 3);
-      case KV_BF16: FA_LAUNCH(64, KV_BF16, 4, 3);
-      case KV_E4M3: FA_LAUNCH(64, KV_E4M3, 4, 3);
-      default: FA_LAUNCH(64, KV_NVFP4, 6, 3);
+      case KV_F16: if (r8) FA_LAUNCH(64, KV_F16, 4, 3, true); FA_LAUNCH(64, KV_F16, 4, 3, false);
+      case KV_BF16: if (r8) FA_LAUNCH(64, KV_BF16, 4, 3, true); FA_LAUNCH(64, KV_BF16, 4, 3, false);
+      case KV_E4M3: if (r8) FA_LAUNCH(64, KV_E4M3, 4, 3, true); FA_LAUNCH(64, KV_E4M3, 4, 3, false);
+      default: if (r8) FA_LAUNCH(64, KV_NVFP4, 6, 3, true); FA_LAUNCH(64, KV_NVFP4, 6, 3, false);
     }
   }
 #undef FA_LAUNCH
