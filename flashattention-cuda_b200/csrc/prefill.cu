@@ -16,6 +16,8 @@
 // kernels/v5_wmma/wmma_attention.cu:229-263): inputs in half precision, fp32 accumulation, optional
 // top-left causal mask (key j masked when j > i, wmma_attention.cu:159), default output fp32.
 
+#include <cstdlib>
+
 #include "sm100.cuh"
 
 namespace fa {
@@ -334,6 +336,10 @@ int launch_prefill(const fa_dense_args* a, const PrefillParams& p, cudaStream_t 
 }  // namespace
 }  // namespace fa
 
+namespace fa {
+int launch_prefill2(const fa_dense_args* a, float scale_log2, cudaStream_t st);   // prefill2.cu
+}
+
 using namespace fa;
 
 extern "C" int fa_dense_fwd(const fa_dense_args* a) {
@@ -354,6 +360,10 @@ extern "C" int fa_dense_fwd(const fa_dense_args* a) {
   p.causal = a->causal; p.out_dtype = a->out_dtype;
   p.scale_log2 = a->softmax_scale * kLog2eF;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+  // Two generations of the kernel exist; the second (two query tiles per CTA, P through tensor memory)
+  // is the default, FA_B200_PREFILL_GEN=1 selects the first.
+  static const int gen = [] { const char* e = getenv("FA_B200_PREFILL_GEN"); return (e && e[0] == '1') ? 1 : 2; }();
+  if (gen == 2) return launch_prefill2(a, p.scale_log2, st);
   if (a->D == 128) return a->dtype == FA_BF16 ? launch_prefill<128, true>(a, p, st) : launch_prefill<128, false>(a, p, st);
   return a->dtype == FA_BF16 ? launch_prefill<64, true>(a, p, st) : launch_prefill<64, false>(a, p, st);
 }

@@ -1,0 +1,361 @@
+// Dense (causal) attention forward, second generation: two 128-row query tiles per CTA that take turns
+// on the tensor core ("ping-pong"), probabilities handed to the second MMA through tensor memory.
+//
+// Warp roles (12 warps, three warpgroups):
+//   warpgroup 0   warp 0: TMA producer (both Q tiles once, then K/V tiles into a 2-stage ring)
+//                 warp 1: TMEM allocation + every tcgen05.mma; warps 2, 3 idle; registers released
+//   warpgroup 1   softmax / correction / epilogue of query tile 0 (thread r owns row r)
+//   warpgroup 2   the same for query tile 1
+// TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).  P_i (fp16 / bf16, two keys
+// per 32-bit column) overwrites the first 64 columns of S_i and is read from there as the A operand
+// of O_i += P_i V (tcgen05.mma with A in tensor memory), so it never touches shared memory.
+// MMA order per key tile j:  PV_j(0)  QK_{j+1}(0)  PV_j(1)  QK_{j+1}(1): while one tile's softmax runs on the
+// CUDA cores, the tensor core works for the other tile.  MMAs of one thread execute in issue order,
+// which is what makes reusing S_i for P_i and then for S_i of the next key tile safe.
+// The running maximum is only raised (and O rescaled) when it grew by more than 2^8, which keeps
+// P <= 256 in half precision and makes TMEM round trips of O rare.
+//
+// Behaviour: as the first-generation kernel (prefill.cu) and the reference's dense entry point
+// (fa_kernels/__init__.py:26-42, kernels/v5_wmma/wmma_attention.cu:229-263).
+
+#include "sm100.cuh"
+
+namespace fa {
+namespace {
+
+using namespace sm100;
+
+constexpr int kP2Threads = 384;
+constexpr uint32_t kP2TmemCols = 512;
+constexpr float kRescaleThreshold = 8.f;     // log2 units
+
+struct Prefill2Params {
+  void* out;
+  float* lse;
+  int* status;
+  int B, H, N_q, N_k;
+  int causal, out_dtype;
+  float scale_log2;
+};
+
+enum { P2_ERR_Q = 21, P2_ERR_KV_FULL = 22, P2_ERR_KV_EMPTY = 23, P2_ERR_S_FULL = 24, P2_ERR_P_READY = 25, P2_ERR_O_DONE = 26 };
+
+template <int NREG>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
+template <int NREG>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
+
+// 32 packed columns (64 half-precision values) of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kP2Threads, 1)
+prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const Prefill2Params p) {
+  constexpr int KB = D / 64;
+  constexpr int TILE_BYTES = 128 * D * 2;
+  constexpr int BLK_BYTES = 128 * 128;
+  constexpr int STAGES = 2;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                                  // [2 query tiles]
+  uint8_t* sK = sQ + 2 * TILE_BYTES;                   // [stage]
+  uint8_t* sV = sK + STAGES * TILE_BYTES;              // [stage]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + STAGES * TILE_BYTES);
+  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, P_READY = 7, O_DONE = 9, NBARS = 11 };
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + NBARS);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wg = warp >> 2;
+  const int n_qt = (p.N_q + 255) / 256;
+  const int qt = n_qt - 1 - (int)blockIdx.x;          // heaviest causal tiles first
+  const int bh = blockIdx.y;
+  const int q0 = qt * 256;
+  const int n_all = (p.N_k + 127) / 128;
+  // key tiles each query tile needs (causal: up to the tile holding its last row)
+  int n_t[2];
+  n_t[0] = p.causal ? min(n_all, (q0 + 127) / 128 + 1) : n_all;
+  n_t[1] = p.causal ? min(n_all, (q0 + 255) / 128 + 1) : n_all;
+  if (q0 + 128 >= p.N_q) n_t[1] = 0;                   // second query tile entirely out of range
+  const int n_max = max(n_t[0], n_t[1]);
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    mbar_init(bar(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(KV_FULL + s), 1);
+      mbar_init(bar(KV_EMPTY + s), 1);
+      mbar_init(bar(S_FULL + s), 1);
+      mbar_init(bar(P_READY + s), 128);
+      mbar_init(bar(O_DONE + s), 1);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(s_tmem), kP2TmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  if (wg == 0) {
+    setmaxnreg_dec<40>();   // 128 x 40 + 256 x 232 = 384 x 168, the register total the CTA was launched with
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      mbar_expect_tx(bar(Q_FULL), 2 * TILE_BYTES);
+      for (int i = 0; i < 2; ++i)
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_3d(smem_u32(sQ + i * TILE_BYTES + kb * BLK_BYTES), &tm_q, kb * 64, q0 + i * 128, bh, bar(Q_FULL));
+      for (int j = 0; j < n_max; ++j) {
+        const int s = j % STAGES;
+        if (j >= STAGES && !mbar_wait(bar(KV_EMPTY + s), ((j / STAGES) - 1) & 1, s_abort, p.status, P2_ERR_KV_EMPTY)) break;
+        mbar_expect_tx(bar(KV_FULL + s), 2 * TILE_BYTES);
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_3d(smem_u32(sK + s * TILE_BYTES + kb * BLK_BYTES), &tm_k, kb * 64, j * 128, bh, bar(KV_FULL + s));
+          tma_load_3d(smem_u32(sV + s * TILE_BYTES + kb * BLK_BYTES), &tm_v, kb * 64, j * 128, bh, bar(KV_FULL + s));
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_qk = idesc_f16(128, 128, BF16, false, false);
+      constexpr uint32_t idesc_pv = idesc_f16(128, D, BF16, false, true);
+      auto issue_qk = [&](int i, int j) {
+        const int s = j % STAGES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * BLK_BYTES + (k & 3) * 32;
+          mma_f16_ss(tmem + i * 128, smem_desc_sw128(smem_u32(sQ + i * TILE_BYTES) + off, 16, 1024),
+                     smem_desc_sw128(smem_u32(sK + s * TILE_BYTES) + off, 16, 1024), idesc_qk, k > 0);
+        }
+        mma_commit(bar(S_FULL + i));
+      };
+      auto issue_pv = [&](int i, int j) {
+        const int s = j % STAGES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // A = P_i in tensor memory: 16 keys = 8 packed columns; B = V [128 keys][D], MN-major
+          const uint64_t b_desc = smem_desc_sw128(smem_u32(sV + s * TILE_BYTES) + k * 2048, BLK_BYTES, 1024);
+          mma_f16_ts(tmem + 256 + i * 128, tmem + i * 128 + k * 8, b_desc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+      };
+      bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, P2_ERR_Q) &&
+                mbar_wait(bar(KV_FULL + 0), 0, s_abort, p.status, P2_ERR_KV_FULL);
+      if (ok) {
+        tc_fence_after();
+        if (n_t[0] > 0) issue_qk(0, 0);
+        if (n_t[1] > 0) issue_qk(1, 0);
+      }
+      for (int j = 0; ok && j < n_max; ++j) {
+        const bool next = (j + 1 < n_max);
+        if (next) {
+          ok = mbar_wait(bar(KV_FULL + ((j + 1) % STAGES)), ((j + 1) / STAGES) & 1, s_abort, p.status, P2_ERR_KV_FULL);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (j < n_t[i]) {
+            ok = mbar_wait(bar(P_READY + i), j & 1, s_abort, p.status, P2_ERR_P_READY);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(i, j);
+            if (j + 1 == n_t[i]) mma_commit(bar(O_DONE + i));
+          }
+          if (i == 1) mma_commit(bar(KV_EMPTY + (j % STAGES)));
+          if (j + 1 < n_t[i]) issue_qk(i, j + 1);
+        }
+      }
+    }
+  } else {
+    setmaxnreg_inc<232>();
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int i = wg - 1;                              // query tile of this warpgroup
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int gi = q0 + i * 128 + row;
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const uint32_t tm_s = tmem + i * 128 + lane_base;
+    const uint32_t tm_o = tmem + 256 + i * 128 + lane_base;
+    const int nt = n_t[i];
+    float m_ref = -INFINITY, l_run = 0.f;              // m_ref: the maximum P and O are currently scaled by
+    bool ok = true;
+    for (int j = 0; j < nt; ++j) {
+      ok = mbar_wait(bar(S_FULL + i), j & 1, s_abort, p.status, P2_ERR_S_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
+      tmem_wait_ld();
+
+      const int k0 = j * 128;
+      const bool need_mask = (k0 + 128 > p.N_k) || (p.causal && k0 + 127 > q0 + i * 128);
+      float mx = -INFINITY;
+      if (need_mask) {
+        const int limit = p.causal ? min(gi, p.N_k - 1) : p.N_k - 1;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          s[c] = (k0 + c <= limit) ? s[c] * p.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, s[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          s[c] *= p.scale_log2;
+          mx = fmaxf(mx, s[c]);
+        }
+      }
+      // raise the reference maximum only when it is more than 2^8 behind
+      const bool raise = (mx > m_ref + kRescaleThreshold) || (m_ref == -INFINITY && mx > -INFINITY);
+      float alpha = 1.f;
+      if (raise) {
+        alpha = fast_exp2(m_ref - mx);                 // m_ref = -inf -> 0
+        m_ref = mx;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 128; ++c) {
+        s[c] = fast_exp2(s[c] - m_use);
+        sum += s[c];
+      }
+      l_run = l_run * alpha + sum;
+      // S_FULL of key tile j implies P V of key tile j-1 has finished (same issuing thread, in order),
+      // so O may be rescaled here
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          tmem_ld32(tm_o + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] *= alpha;
+          tmem_st32(tm_o + c * 32, o);
+        }
+      }
+      // P -> tensor memory over the first 64 columns of S_i: column c holds keys 2c, 2c+1
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          pk[c] = BF16 ? pack_bf2(s[h * 64 + 2 * c], s[h * 64 + 2 * c + 1]) : pack_h2(s[h * 64 + 2 * c], s[h * 64 + 2 * c + 1]);
+        tmem_st32u(tm_s + h * 32, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(P_READY + i));
+    }
+    if (ok && nt > 0) ok = mbar_wait(bar(O_DONE + i), 0, s_abort, p.status, P2_ERR_O_DONE);
+    if (ok && nt > 0) {
+      tc_fence_after();
+      const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      const bool valid = gi < p.N_q;
+      const int64_t orow = (int64_t)bh * p.N_q + gi;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        tmem_ld32(tm_o + c * 32, o);
+        tmem_wait_ld();
+        if (valid) {
+          if (p.out_dtype == FA_F32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow * D + c * 32);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              dst[e] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv, o[4 * e + 2] * inv, o[4 * e + 3] * inv);
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + orow * D + c * 32);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              uint4 v;
+              if (p.out_dtype == FA_BF16) {
+                v.x = pack_bf2(o[8 * e] * inv, o[8 * e + 1] * inv); v.y = pack_bf2(o[8 * e + 2] * inv, o[8 * e + 3] * inv);
+                v.z = pack_bf2(o[8 * e + 4] * inv, o[8 * e + 5] * inv); v.w = pack_bf2(o[8 * e + 6] * inv, o[8 * e + 7] * inv);
+              } else {
+                v.x = pack_h2(o[8 * e] * inv, o[8 * e + 1] * inv); v.y = pack_h2(o[8 * e + 2] * inv, o[8 * e + 3] * inv);
+                v.z = pack_h2(o[8 * e + 4] * inv, o[8 * e + 5] * inv); v.w = pack_h2(o[8 * e + 6] * inv, o[8 * e + 7] * inv);
+              }
+              dst[e] = v;
+            }
+          }
+        }
+      }
+      if (valid && p.lse) p.lse[orow] = (l_run > 0.f) ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) __nanosleep(200000);   // after a timed-out wait: give copies still in flight time to land
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kP2TmemCols);
+  }
+}
+
+}  // namespace
+
+template <int D, bool BF16>
+static int launch_prefill2_t(const fa_dense_args* a, float scale_log2, cudaStream_t st) {
+  CUtensorMap tq, tk, tv;
+  const int dt = BF16 ? FA_BF16 : FA_F16;
+  const uint64_t BH = (uint64_t)a->B * a->H;
+  const uint32_t box[3] = {64, 128, 1};
+  {
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)a->N_q, BH};
+    const uint64_t strides[2] = {(uint64_t)D * 2, (uint64_t)a->N_q * D * 2};
+    int rc = encode_tensor_map(&tq, dt, 3, const_cast<void*>(a->q), dims, strides, box, 1);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)a->N_k, BH};
+    const uint64_t strides[2] = {(uint64_t)D * 2, (uint64_t)a->N_k * D * 2};
+    int rc = encode_tensor_map(&tk, dt, 3, const_cast<void*>(a->k), dims, strides, box, 1);
+    if (rc) return rc;
+    rc = encode_tensor_map(&tv, dt, 3, const_cast<void*>(a->v), dims, strides, box, 1);
+    if (rc) return rc;
+  }
+  Prefill2Params p{};
+  p.out = a->out; p.lse = a->lse; p.status = a->status;
+  p.B = a->B; p.H = a->H; p.N_q = a->N_q; p.N_k = a->N_k;
+  p.causal = a->causal; p.out_dtype = a->out_dtype; p.scale_log2 = scale_log2;
+  constexpr int TILE = 128 * D * 2;
+  constexpr int SMEM = TILE * 6 + 256 + 1024;
+  auto kern = prefill2_kernel<D, BF16>;
+  static int configured_device = -1;
+  int dev = 0;
+  FA_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    FA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured_device = dev;
+  }
+  dim3 grid((unsigned)((a->N_q + 255) / 256), (unsigned)BH);
+  kern<<<grid, kP2Threads, SMEM, st>>>(tq, tk, tv, p);
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
+}
+
+// Entry used by fa_dense_fwd (prefill.cu) after it has validated the arguments.
+int launch_prefill2(const fa_dense_args* a, float scale_log2, cudaStream_t st) {
+  if (a->D == 128) return a->dtype == FA_BF16 ? launch_prefill2_t<128, true>(a, scale_log2, st) : launch_prefill2_t<128, false>(a, scale_log2, st);
+  return a->dtype == FA_BF16 ? launch_prefill2_t<64, true>(a, scale_log2, st) : launch_prefill2_t<64, false>(a, scale_log2, st);
+}
+
+}  // namespace fa
