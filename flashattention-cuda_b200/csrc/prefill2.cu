@@ -18,6 +18,8 @@
 // Behaviour: as the first-generation kernel (prefill.cu) and the reference's dense entry point
 // (fa_kernels/__init__.py:26-42, kernels/v5_wmma/wmma_attention.cu:229-263).
 
+#include <cstdlib>
+
 #include "sm100.cuh"
 
 namespace fa {
@@ -58,7 +60,50 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[3
       : "memory");
 }
 
-template <int D, bool BF16>
+// ---- packed fp32 pairs (two fp32 lanes in one 64-bit register: fma / add issue once for two values) ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// 2^x for a pair on the FMA pipe instead of the MUFU: x = n + f with n = round(x), f in [-0.5, 0.5];
+// 2^f by a cubic (max relative error 7.5e-5, below the half-precision rounding of P), 2^n by adding n to
+// the exponent field.  Inputs are clamped at -125 (masked scores arrive as -inf).
+__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  const uint64_t xc = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t t = add2(xc, pack2(12582912.f, 12582912.f));            // 1.5 * 2^23: low mantissa bits = n
+  const uint64_t n = add2(t, pack2(-12582912.f, -12582912.f));
+  const uint64_t f = fma2(n, pack2(-1.f, -1.f), xc);
+  uint64_t q = fma2(f, pack2(0.055170976f, 0.055170976f), pack2(0.24260971f, 0.24260971f));
+  q = fma2(q, f, pack2(0.69326097f, 0.69326097f));
+  q = fma2(q, f, pack2(0.99992818f, 0.99992818f));
+  float q0, q1, t0, t1;
+  unpack2(q, q0, q1);
+  unpack2(t, t0, t1);
+  const float r0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  const float r1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+  return pack2(r0, r1);
+}
+
+template <int D, bool BF16, int POLY>
 __global__ void __launch_bounds__(kP2Threads, 1)
 prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const Prefill2Params p) {
@@ -207,21 +252,25 @@ prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       const int k0 = j * 128;
       const bool need_mask = (k0 + 128 > p.N_k) || (p.causal && k0 + 127 > q0 + i * 128);
-      float mx = -INFINITY;
+      // scores stay unscaled until the exponent: max commutes with the (positive) scale, and
+      // scale * s - m is one fused multiply-add per pair
       if (need_mask) {
         const int limit = p.causal ? min(gi, p.N_k - 1) : p.N_k - 1;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          s[c] = (k0 + c <= limit) ? s[c] * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, s[c]);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          s[c] *= p.scale_log2;
-          mx = fmaxf(mx, s[c]);
-        }
+        for (int c = 0; c < 128; ++c)
+          if (k0 + c > limit) s[c] = -INFINITY;
       }
+      // four independent chains each for the maximum and the sum: one warp per scheduler per query
+      // tile is all the parallelism there is, so dependent chains of 64 operations would set the pace
+      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 128; c += 8) {
+        mxa = max3(mxa, s[c], s[c + 1]);
+        mxb = max3(mxb, s[c + 2], s[c + 3]);
+        mxc = max3(mxc, s[c + 4], s[c + 5]);
+        mxd = max3(mxd, s[c + 6], s[c + 7]);
+      }
+      float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd)) * p.scale_log2;
       // raise the reference maximum only when it is more than 2^8 behind
       const bool raise = (mx > m_ref + kRescaleThreshold) || (m_ref == -INFINITY && mx > -INFINITY);
       float alpha = 1.f;
@@ -230,12 +279,25 @@ prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         m_ref = mx;
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float sum = 0.f;
+      const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_use, -m_use);
+      uint64_t sums[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
-      for (int c = 0; c < 128; ++c) {
-        s[c] = fast_exp2(s[c] - m_use);
-        sum += s[c];
+      for (int c = 0; c < 128; c += 2) {
+        const uint64_t x2 = fma2(pack2(s[c], s[c + 1]), sc2, nm2);
+        uint64_t p2;
+        if (((c >> 1) & 7) < POLY) {                   // POLY of every 8 pairs go to the FMA pipe
+          p2 = exp2_poly2(x2);
+        } else {
+          float x0, x1;
+          unpack2(x2, x0, x1);
+          p2 = pack2(fast_exp2(x0), fast_exp2(x1));
+        }
+        sums[(c >> 1) & 3] = add2(sums[(c >> 1) & 3], p2);
+        unpack2(p2, s[c], s[c + 1]);
       }
+      float sum_lo, sum_hi;
+      unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), sum_lo, sum_hi);
+      const float sum = sum_lo + sum_hi;
       l_run = l_run * alpha + sum;
       // S_FULL of key tile j implies P V of key tile j-1 has finished (same issuing thread, in order),
       // so O may be rescaled here
@@ -312,7 +374,7 @@ prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 }  // namespace
 
-template <int D, bool BF16>
+template <int D, bool BF16, int POLY>
 static int launch_prefill2_t(const fa_dense_args* a, float scale_log2, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   const int dt = BF16 ? FA_BF16 : FA_F16;
@@ -338,7 +400,7 @@ static int launch_prefill2_t(const fa_dense_args* a, float scale_log2, cudaStrea
   p.causal = a->causal; p.out_dtype = a->out_dtype; p.scale_log2 = scale_log2;
   constexpr int TILE = 128 * D * 2;
   constexpr int SMEM = TILE * 6 + 256 + 1024;
-  auto kern = prefill2_kernel<D, BF16>;
+  auto kern = prefill2_kernel<D, BF16, POLY>;
   static int configured_device = -1;
   int dev = 0;
   FA_CUDA_OK(cudaGetDevice(&dev));
@@ -353,9 +415,24 @@ static int launch_prefill2_t(const fa_dense_args* a, float scale_log2, cudaStrea
 }
 
 // Entry used by fa_dense_fwd (prefill.cu) after it has validated the arguments.
+// FA_B200_PREFILL_POLY = 0, 2 or 4 selects how many of every 8 exponent pairs are evaluated by the
+// polynomial on the FMA pipe (the rest on the MUFU).  Measured on B=4 H=32 N=4096 d=128: 0 -> 660 us,
+// 2 -> 667 us, 4 -> 681 us: the kernel is short of issue slots, not of MUFU throughput, so 0 is the default.
 int launch_prefill2(const fa_dense_args* a, float scale_log2, cudaStream_t st) {
-  if (a->D == 128) return a->dtype == FA_BF16 ? launch_prefill2_t<128, true>(a, scale_log2, st) : launch_prefill2_t<128, false>(a, scale_log2, st);
-  return a->dtype == FA_BF16 ? launch_prefill2_t<64, true>(a, scale_log2, st) : launch_prefill2_t<64, false>(a, scale_log2, st);
+  static const int poly = [] { const char* e = getenv("FA_B200_PREFILL_POLY"); return e ? atoi(e) : 0; }();
+#define FA_P2(D_, BF_)                                                          \
+  switch (poly) {                                                               \
+    case 2: return launch_prefill2_t<D_, BF_, 2>(a, scale_log2, st);            \
+    case 4: return launch_prefill2_t<D_, BF_, 4>(a, scale_log2, st);            \
+    default: return launch_prefill2_t<D_, BF_, 0>(a, scale_log2, st);           \
+  }
+  if (a->D == 128) {
+    if (a->dtype == FA_BF16) { FA_P2(128, true) }
+    FA_P2(128, false)
+  }
+  if (a->dtype == FA_BF16) { FA_P2(64, true) }
+  FA_P2(64, false)
+#undef FA_P2
 }
 
 }  // namespace fa
