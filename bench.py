@@ -229,7 +229,7 @@ def run_ours(args):
 
 # DRAM bytes per launch of the decode kernel from the committed ncu capture
 # (profiles/paged_decode_fp16_config3.md), or None until one exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+TRAFFIC_BYTES_PER_LAUNCH = 1312048592   # 1.303458 GB read + 8.59 MB written
 
 
 def _cpu_pass(w, max_seconds):
