@@ -232,10 +232,20 @@ def run_ours(args):
 TRAFFIC_BYTES_PER_LAUNCH = 1312048592   # 1.303458 GB read + 8.59 MB written
 
 
+def _use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm should use the cores this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(n, 1))
+
+
 def _cpu_pass(w, max_seconds):
     """One pass of the reference CPU path over the batch (or as much of it as fits the time bound).
     Returns (seconds, kv_bytes_processed, sequences_done)."""
     from oracle import cpu_reference as R
+    _use_all_host_threads()
     q = w["q"].float().cpu()
     kp, vp = w["k_pool"].cpu(), w["v_pool"].cpu()
     bt = w["block_table_host"]

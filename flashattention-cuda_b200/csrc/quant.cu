@@ -187,6 +187,32 @@ __global__ void paged_move_kernel(uint8_t* __restrict__ dense, uint8_t* __restri
   }
 }
 
+// ---- NVFP4 scale-granularity study: quantise-dequantise in fp32 at one scale per tensor, per channel
+// (last-dim index) or per token (row) — fa_kernels/nvfp4_recipes.py:42-73 of the reference -------------
+// amax[] holds float bit patterns: [1] (tensor), [d] (channel) or [rows] (token)
+__global__ void absmax_axis_kernel(const float* __restrict__ x, int64_t rows, int d, int mode, uint32_t* __restrict__ amax) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < rows * d; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = fabsf(x[i]);
+    const uint32_t bits = (v != v) ? 0x7fc00000u : __float_as_uint(v);
+    const int64_t slot = mode == 0 ? 0 : (mode == 1 ? (i % d) : (i / d));
+    atomicMax(amax + slot, bits);
+  }
+}
+__global__ void fake_quant_apply_kernel(const float* __restrict__ x, int64_t rows, int d, int mode, int e4m3_scale,
+                                        const uint32_t* __restrict__ amax, float* __restrict__ out) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < rows * d; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t slot = mode == 0 ? 0 : (mode == 1 ? (i % d) : (i / d));
+    float scale = fmaxf(__fdiv_rn(__uint_as_float(amax[slot]), 6.0f), 1e-12f);
+    if (e4m3_scale) scale = fmaxf(e4m3_to_f32(f32_to_e4m3_rne(scale)), 1e-12f);
+    const float y = __fdiv_rn(x[i], scale);
+    const uint32_t code = e2m1_code(y);
+    const float mag = kE2M1Levels[code & 7];
+    // torch.sign: 0 for +-0, NaN stays NaN
+    const float sgn = (y != y) ? y : ((y > 0.f) ? 1.f : ((y < 0.f) ? -1.f : 0.f));
+    out[i] = __fmul_rn(__fmul_rn(sgn, mag), scale);
+  }
+}
+
 inline int grid_for(int64_t work, int threads, int sms) {
   const int64_t blocks = (work + threads - 1) / threads;
   return (int)std::max<int64_t>(1, std::min<int64_t>(blocks, (int64_t)sms * 8));
@@ -294,4 +320,22 @@ extern "C" int fa_paged_scatter(const void* dense, void* pool, const int32_t* bl
 extern "C" int fa_paged_gather(const void* pool, void* dense, const int32_t* block_table, int B, int H, int N, int row_bytes,
                                int page_size, int n_logical, int num_blocks, void* stream) {
   return paged_move(false, dense, const_cast<void*>(pool), block_table, B, H, N, row_bytes, page_size, n_logical, num_blocks, stream);
+}
+
+extern "C" int fa_fake_quant_e2m1(const float* x, int64_t rows, int d, int granularity, int e4m3_scale, float* out,
+                                  void* scratch, size_t scratch_bytes, void* stream) {
+  FA_CHECK_ARG(x && out && scratch, "fa_fake_quant_e2m1: null pointer");
+  FA_CHECK_ARG(rows >= 1 && d >= 1, "fa_fake_quant_e2m1: bad sizes");
+  FA_CHECK_ARG(granularity >= 0 && granularity <= 2, "fa_fake_quant_e2m1: granularity must be 0 (tensor), 1 (channel) or 2 (token)");
+  const int64_t n_amax = granularity == 0 ? 1 : (granularity == 1 ? d : rows);
+  if (scratch_bytes < (size_t)n_amax * 4) return fail(FA_ERR_WORKSPACE, "fa_fake_quant_e2m1: scratch %zu B < %lld B", scratch_bytes, (long long)n_amax * 4);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int sms = std::max(device_sm_count(), 1);
+  uint32_t* amax = reinterpret_cast<uint32_t*>(scratch);
+  FA_CUDA_OK(cudaMemsetAsync(amax, 0, (size_t)n_amax * 4, st));
+  const int g = grid_for(rows * d, 256, sms);
+  absmax_axis_kernel<<<g, 256, 0, st>>>(x, rows, d, granularity, amax);
+  fake_quant_apply_kernel<<<g, 256, 0, st>>>(x, rows, d, granularity, e4m3_scale, amax, out);
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
 }

@@ -28,10 +28,13 @@ def _require(cond: bool, msg: str) -> None:
 
 
 def sm_count(device) -> int:
-    n = C.c_int(0)
-    with torch.cuda.device(device):
-        _lib.check(_lib.load().fa_device_sm_count(C.byref(n)), "fa_device_sm_count")
-    return n.value
+    key = str(device)
+    if key not in _sm_count:
+        n = C.c_int(0)
+        with torch.cuda.device(device):
+            _lib.check(_lib.load().fa_device_sm_count(C.byref(n)), "fa_device_sm_count")
+        _sm_count[key] = n.value
+    return _sm_count[key]
 
 
 def plan(seq_lens, n_k: int, B: int, H_kv: int, rows: int, page_size: int, device, chunk_hint: int = 0):
@@ -49,18 +52,42 @@ def plan(seq_lens, n_k: int, B: int, H_kv: int, rows: int, page_size: int, devic
         lens_arr = (C.c_int32 * B)(*seq_lens)
         lens_ptr = C.cast(lens_arr, C.c_void_p)
     cap = lib.fa_decode_plan_max_items(lens_ptr, int(n_k), B, page_size)
-    host = torch.empty((cap, 8), dtype=torch.int32, pin_memory=True)
+    host, done = _staging(device, cap)
     n_items, max_range = C.c_int(0), C.c_int(0)
     _lib.check(lib.fa_decode_plan(lens_ptr, int(n_k), B, H_kv, rows, page_size, sm_count(device), chunk_hint,
                                   host.data_ptr(), cap, C.byref(n_items), C.byref(max_range)), "fa_decode_plan")
     n = n_items.value
-    items = host[:n].to(device, non_blocking=True)
+    items = torch.empty((n, 8), dtype=torch.int32, device=device)
+    items.copy_(host[:n], non_blocking=True)
+    done.record(torch.cuda.current_stream(device))
     n_slots = n if n > B else 0
-    out = (items, n, n_slots, max_range.value, host)   # keep the pinned buffer alive with the entry
+    out = (items, n, n_slots, max_range.value, None)
     if len(_plan_cache) >= _PLAN_CACHE_MAX:
         _plan_cache.pop(next(iter(_plan_cache)))
     _plan_cache[key] = out
     return out
+
+
+_STAGING_SLOTS = 8
+_staging_ring: dict = {}
+_sm_count: dict = {}
+
+
+def _staging(device, cap: int):
+    """A pinned host buffer for one plan upload, from a small per-device ring.  Pinned allocations are
+    slow, so buffers are reused; each slot carries the event of its last upload and is only handed out
+    again after that copy has finished."""
+    key = str(device)
+    ring = _staging_ring.setdefault(key, {"next": 0, "slots": [None] * _STAGING_SLOTS})
+    i = ring["next"]
+    ring["next"] = (i + 1) % _STAGING_SLOTS
+    slot = ring["slots"][i]
+    if slot is None or slot[0].shape[0] < cap:
+        slot = (torch.empty((max(cap, 1024), 8), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+        ring["slots"][i] = slot
+    else:
+        slot[1].synchronize()
+    return slot
 
 
 def workspace(device, nbytes: int, n_counters: int):

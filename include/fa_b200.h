@@ -279,6 +279,14 @@ FA_API int fa_paged_scatter(const void* dense, void* pool, const int32_t* block_
 FA_API int fa_paged_gather(const void* pool, void* dense, const int32_t* block_table, int B, int H, int N, int row_bytes,
                            int page_size, int n_logical, int num_blocks, void* stream);
 
+/* Quantise-dequantise to signed E2M1 levels in fp32 with one scale = amax / 6 per tensor (0), per channel =
+ * last-dimension index (1) or per token = row (2), the scale optionally rounded through E4M3 —
+ * `fake_quant_nvfp4` for the granularities "tensor" / "channel" / "token" of the reference's
+ * fa_kernels/nvfp4_recipes.py:42-73 ("block16" is fa_quantize_nvfp4 + fa_dequantize_nvfp4).
+ * x, out: device float32 [rows, d]; scratch: device, 4 bytes per scale. */
+FA_API int fa_fake_quant_e2m1(const float* x, int64_t rows, int d, int granularity, int e4m3_scale, float* out,
+                              void* scratch, size_t scratch_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -146,3 +146,33 @@ def test_builders_feed_the_decode_kernels():
     out = nvfp4_attention(q.cuda(), kp, km, vp, vm, bt, page, n_k, sk, sv)
     assert_close(out, O.gqa_attention_ref(qn, O.dequantize_nvfp4(*O.quantize_nvfp4(kn)), O.dequantize_nvfp4(*O.quantize_nvfp4(vn))),
                  what="nvfp4")
+
+
+@pytest.mark.parametrize("gran", ["tensor", "block16", "channel", "token"])
+@pytest.mark.parametrize("e4m3_scale", [True, False])
+def test_fake_quant_granularities_bit_exact(gran, e4m3_scale, golden):
+    """The scale-granularity study's quantise-dequantise against the fixture made by the reference's
+    own nvfp4_recipes.fake_quant_nvfp4 (outlier channel and outlier token included)."""
+    from fa_kernels.nvfp4_recipes import fake_quant_nvfp4
+    g = golden("recipes.npz")
+    got = fake_quant_nvfp4(torch.from_numpy(g["k"]).cuda(), gran, e4m3_scale=e4m3_scale)
+    want = g[f"fq_k_{gran}" if e4m3_scale else f"fq_k_{gran}_fp32scale"]
+    np.testing.assert_array_equal(_np(got), want)
+
+
+def test_recipe_rmse_close_to_reference_numbers():
+    """attn_rmse / fp8_attn_rmse run the attention on the tensor-core kernel (inputs rounded to fp16),
+    so they match the oracle's fp64 figures to a few percent, not bit for bit."""
+    from fa_kernels.nvfp4_recipes import attn_rmse, fp8_attn_rmse
+    g = torch.Generator().manual_seed(27)
+    q = torch.randn(1, 4, 128, 64, generator=g)
+    k = torch.randn(1, 2, 256, 64, generator=g)
+    v = torch.randn(1, 2, 256, 64, generator=g)
+    k[..., 5] *= 10.0
+    v[:, :, 7, :] *= 10.0
+    for kw in (dict(k_gran="block16", v_gran="block16"), dict(k_gran="channel", v_gran="token")):
+        got = attn_rmse(q.cuda(), k.cuda(), v.cuda(), **kw)
+        want = O.attn_rmse(q.numpy(), k.numpy(), v.numpy(), **kw)
+        assert abs(got - want) <= 0.05 * want + 2e-4, (kw, got, want)
+    got, want = fp8_attn_rmse(q.cuda(), k.cuda(), v.cuda()), O.fp8_attn_rmse(q.numpy(), k.numpy(), v.numpy())
+    assert abs(got - want) <= 0.05 * want + 2e-4
