@@ -14,7 +14,9 @@
 // Reference behaviour: kernels/v11_mla/mla_attention.cu:104-258 (row m -> head, i_q; mask key j when
 // j > i_q + q_offset; output O_latent [B,h_q,N_q,DV] fp32) and :320-409 (argument checks).
 
+#include <algorithm>
 #include <climits>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -475,12 +477,27 @@ int launch_mla(const MlaParams& p, int n_items, int row_tiles, cudaStream_t st) 
 }  // namespace
 }  // namespace fa
 
+namespace fa {
+// tensor-core path (mla_tc.cu)
+bool mla_tc_applicable(const fa_mla_args* a);
+size_t mla_tc_workspace_bytes(int n_slots, int M);
+size_t mla_tc_counters_len(int B, int M);
+int launch_mla_tc(const fa_mla_args* a, cudaStream_t st);
+}  // namespace fa
+
 using namespace fa;
 
 extern "C" size_t fa_mla_counters_len(int B, int H_q, int N_q) {
   const int row_tiles = (H_q * N_q + kMlaRows - 1) / kMlaRows;
-  return (size_t)B * row_tiles + 1;
+  return std::max((size_t)B * row_tiles + 1, mla_tc_counters_len(B, H_q * N_q));
 }
+
+extern "C" size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV) {
+  return std::max((size_t)n_slots * H_q * N_q * (DV + 1) * 4, mla_tc_workspace_bytes(n_slots, H_q * N_q));
+}
+
+// Largest key range (in keys, a multiple of 64) one CTA of the tensor-core kernel can take at this page size.
+extern "C" int fa_mla_tc_max_range(int page_size) { return (126 * page_size) / 64 * 64; }
 
 extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   FA_CHECK_ARG(a != nullptr, "fa_mla_decode_fwd: null args");
@@ -515,6 +532,14 @@ extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   const size_t n_counters = fa_mla_counters_len(a->B, a->H_q, a->N_q);
   FA_CHECK_ARG(a->counters != nullptr, "counters must be non-null");
   if (a->counters_len < n_counters) return fail(FA_ERR_WORKSPACE, "counters hold %zu ints < %zu", a->counters_len, n_counters);
+
+  // bf16 (576, 512) latents on 64-token-aligned pages run on tcgen05 unless FA_B200_MLA_TC=0
+  static const bool tc_enabled = [] { const char* e = getenv("FA_B200_MLA_TC"); return !(e && e[0] == '0'); }();
+  if (tc_enabled && a->engine_hint != 2 && mla_tc_applicable(a)) {
+    if (a->workspace_bytes < mla_tc_workspace_bytes(a->n_slots, M))
+      return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, mla_tc_workspace_bytes(a->n_slots, M));
+    return launch_mla_tc(a, reinterpret_cast<cudaStream_t>(a->stream));
+  }
 
   MlaParams p{};
   p.q = reinterpret_cast<const uint16_t*>(a->q);

@@ -28,16 +28,18 @@ class MlaArgs(C.Structure):
         ("items", C.c_void_p), ("n_items", C.c_int), ("n_slots", C.c_int), ("max_range_keys", C.c_int),
         ("out", C.c_void_p), ("out_dtype", C.c_int), ("lse", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("counters", C.c_void_p), ("counters_len", C.c_size_t), ("stream", C.c_void_p),
+        ("counters", C.c_void_p), ("counters_len", C.c_size_t), ("stream", C.c_void_p), ("engine_hint", C.c_int),
     ]
 
 
 def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, scale_l, scale, causal=False,
-               q_offset=0, *, out_dtype=None, return_lse=False, chunk_hint=0, out=None, lse_out=None):
+               q_offset=0, *, out_dtype=None, return_lse=False, chunk_hint=0, out=None, lse_out=None, engine_hint=0):
     lib = _lib.load()
     lib.fa_mla_counters_len.restype = C.c_size_t
     lib.fa_mla_counters_len.argtypes = [C.c_int] * 3
     lib.fa_mla_decode_fwd.argtypes = [C.POINTER(MlaArgs)]
+    lib.fa_mla_workspace_bytes.restype = C.c_size_t
+    lib.fa_mla_workspace_bytes.argtypes = [C.c_int] * 4
     _require(q.is_cuda and l_pool.is_cuda and block_table.is_cuda, "q, l_pool, l_scale, block_table must be CUDA tensors")
     _require(q.dim() == 4, "q (q_absorbed) must be [B,H_q,N_q,DQK]")
     _require(l_pool.dim() == 4, "l_pool must be [num_blocks, page_size, H_kv=1, *]")
@@ -103,8 +105,14 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
         q_offset = 0
 
     rows32 = 16 * ((H_q * N_q + 31) // 32)          # the planner counts 16-row tiles; this kernel uses 32
+    tc_shape = (fmt == FA_BF16 and DQK == 576 and DV == 512 and page_size % 64 == 0
+                and page_size & (page_size - 1) == 0 and engine_hint != 2)
+    if tc_shape:
+        # the tensor-core kernel stages at most 128 block-table entries per CTA: bound the key ranges
+        cap = lib.fa_mla_tc_max_range(page_size)
+        chunk_hint = min(int(chunk_hint), cap) if chunk_hint else (cap if n_max > cap else 0)
     items, n_items, n_slots, max_range, _ = _decode.plan(lens, n_max, B, 1, rows32, page_size, dev, int(chunk_hint))
-    ws, cnt = _decode.workspace(dev, lib.fa_decode_workspace_bytes(n_slots, H_q, N_q, DV),
+    ws, cnt = _decode.workspace(dev, lib.fa_mla_workspace_bytes(n_slots, H_q, N_q, DV),
                                 lib.fa_mla_counters_len(B, H_q, N_q))
     a = MlaArgs()
     a.q, a.q_dtype = q.data_ptr(), _TORCH_TO_FA[q_t]
@@ -122,6 +130,7 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.counters, a.counters_len = cnt.data_ptr(), cnt.numel()
     a.stream = torch.cuda.current_stream(dev).cuda_stream
+    a.engine_hint = int(engine_hint)
     with torch.cuda.device(dev):
         _lib.check(lib.fa_mla_decode_fwd(C.byref(a)), "fa_mla_decode_fwd")
     return (out, lse) if return_lse else out

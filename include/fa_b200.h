@@ -214,8 +214,9 @@ FA_API int fa_dense_fwd(const fa_dense_args* args);
  *             per-token scales of an E4M3 latent (multiply l_scale)
  *   (DQK, DV) in {(576,512), (160,128), (96,64)} as in kernels/v11_mla/mla_attention.cu:383-397.
  * Plan, workspace and counters as for fa_paged_decode_fwd, with H_kv = 1 and 32-row tiles: call
- * fa_decode_plan(..., H_kv = 1, rows = 16 * ceil(H_q * N_q / 32), ...), workspace bytes =
- * fa_decode_workspace_bytes(n_slots, H_q, N_q, DV), counters = fa_mla_counters_len(B, H_q, N_q).
+ * fa_decode_plan(..., H_kv = 1, rows = 16 * ceil(H_q * N_q / 32), chunk_hint <= fa_mla_tc_max_range(page_size)
+ * to allow the tcgen05 kernel), workspace bytes = fa_mla_workspace_bytes(n_slots, H_q, N_q, DV), counters =
+ * fa_mla_counters_len(B, H_q, N_q).
  * ---------------------------------------------------------------------------------------------- */
 typedef struct fa_mla_args {
   const void* q;
@@ -246,8 +247,12 @@ typedef struct fa_mla_args {
   int32_t* counters;
   size_t counters_len;
   void* stream;
+  int engine_hint;   /* 0 = choose; 2 = force the mma.sync kernel (the tcgen05 kernel needs a bf16 (576, 512)
+                        latent, page_size a power of two >= 64 and key ranges <= fa_mla_tc_max_range) */
 } fa_mla_args;
 FA_API size_t fa_mla_counters_len(int B, int H_q, int N_q);
+FA_API size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV);
+FA_API int fa_mla_tc_max_range(int page_size);
 FA_API int fa_mla_decode_fwd(const fa_mla_args* args);
 
 /* ------------------------------------------------------------------------------------------------

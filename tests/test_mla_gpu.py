@@ -158,3 +158,47 @@ def test_mla_argument_checks():
         mla_attention(torch.zeros(1, 16, 1, 128, device="cuda", dtype=torch.float16),
                       torch.zeros(2, 64, 1, 64, device="cuda", dtype=torch.uint8),
                       torch.zeros(2, 64, 1, 8, device="cuda", dtype=torch.uint8), bt, 64, 100, 64, 1.0)
+
+
+# ----------------------------------------------------------------- tensor-core (tcgen05) MLA path
+def _bf16_latent(lens, page_size, seed, scale=0.1, DQK=576):
+    lats = [randn((1, n, DQK), seed * 10 + i, torch.float32, scale)[1].astype(np.float32) for i, n in enumerate(lens)]
+    stored = [torch.from_numpy(a).bfloat16() for a in lats]
+    pool, bt, _ = paged_varlen([s.view(torch.int16).numpy() for s in stored], page_size, seed)
+    return [s.float().numpy() for s in stored], torch.from_numpy(pool).view(torch.bfloat16).cuda(), dev(bt)
+
+
+@pytest.mark.parametrize("h_q", [128, 16, 40])
+@pytest.mark.parametrize("page_size", [64, 256])
+def test_mla_tensor_core_path_matches_oracle_and_legacy_kernel(h_q, page_size):
+    """bf16 (576, 512) latents on 64-aligned pages run on tcgen05; same inputs through the mma.sync kernel
+    (engine_hint=2) and the oracle.  Lengths cover one tile, ragged tails, an empty sequence and a context
+    long enough to be split (> 126 pages of 64)."""
+    from fa_kernels._mla import mla_decode
+    lens = [20000, 64, 4097, 1, 0, 777, 8064, 8065]
+    B = len(lens)
+    q_t, q = randn((B, h_q, 1, 576), 71, torch.bfloat16)
+    hat, l_pool, bt = _bf16_latent(lens, page_size, 71)
+    scale = 1.0 / 576 ** 0.5
+    out, lse = mla_decode(q_t.cuda(), l_pool, None, bt, page_size, lens, 512, 1.0, scale, return_lse=True)
+    legacy = mla_decode(q_t.cuda(), l_pool, None, bt, page_size, lens, 512, 1.0, scale, engine_hint=2)
+    torch.cuda.synchronize()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert (out[b] == 0).all() and torch.isneginf(lse[b]).all()
+            continue
+        ref, ref_lse = O.mla_attention_ref(q[b:b + 1], hat[b][None], 512, return_lse=True)
+        assert_close(out[b:b + 1], ref, what=f"mla tc seq {b}")
+        np.testing.assert_allclose(lse[b:b + 1].cpu().numpy(), ref_lse, atol=3e-3, rtol=1e-3)
+    assert_close(out, legacy.cpu().numpy(), what="tc vs mma.sync")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_mla_tensor_core_square_prefill(causal):
+    from fa_kernels import mla_attention
+    h_q, N, page_size = 4, 300, 64
+    q_t, q = randn((2, h_q, N, 576), 72, torch.bfloat16)
+    hat, l_pool, bt = _bf16_latent([N, N], page_size, 72)
+    out = mla_attention(q_t.cuda(), l_pool, None, bt, page_size, N, 512, 1.0, causal=causal, q_offset=0)
+    for b in range(2):
+        assert_close(out[b:b + 1], O.mla_attention_ref(q[b:b + 1], hat[b][None], 512, causal=causal), what="mla tc square")
