@@ -2,21 +2,30 @@
 //
 // The 128 x 512 fp32 output of 128 heads would fill all 512 TMEM columns, so the value dimension is cut
 // in two: CTA (range, dvh) accumulates O[:, dvh*256 : dvh*256+256] and both halves compute the scores.
-// Per CTA, per 64-key latent tile (TMA, nine 64-column blocks, 128-byte swizzle, 2-stage ring):
-//   S = Q L^T   M=128 heads, N=64 keys, K=576: the first 256 query dims live in tensor memory (A operand
-//               from TMEM, so they cost no shared-memory bandwidth), the other 320 in shared memory
-//   softmax     thread r owns head r: tcgen05.ld of its 64 scores, lazy-rescaled running maximum, P written
+// Per CTA, per 32-key latent tile (TMA, nine 64-column blocks, 128-byte swizzle, 4-stage ring: with one
+// CTA per SM the loads of three tiles have to be in flight to cover the TMA latency):
+//   S = Q L^T   M=128 heads, N=32 keys, K=576: the first 384 query dims live in tensor memory (A operand
+//               from TMEM, so they cost no shared-memory bandwidth), the other 192 in shared memory
+//   softmax     thread r owns head r: tcgen05.ld of its 32 scores, lazy-rescaled running maximum, P written
 //               as packed bf16 over the S columns
 //   O += P L_v  A = P from TMEM, B = the tile's value columns as an MN-major operand, N = 256
-// TMEM columns: O [0,256)  S0 [256,320)  S1 [320,384)  Q [384,512).
+// TMEM columns: O [0,256)  S0 [256,288)  S1 [288,320)  Q [320,512).
 // Warps: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2..5 = softmax / epilogue (lane quadrant = warp % 4).
 // Rows pack m = h * N_q + i_q so that a sequence's query rows are contiguous for the Q tensor map.
 // Splits of a sequence are merged by the last CTA to arrive, per value half.
+//
+// Measured anatomy of one 32-key tile (clock64 trace of one CTA, 128 heads, 8000-key sequences): period
+// 3040 cycles, of which the softmax warps spend 2340 waiting for the scores, 30 in tcgen05.ld, 520 computing
+// and 40 in tcgen05.st; the MMA thread waits 145 cycles for P.  The tensor pipe sets the pace: the 36
+// k-steps of Q L^T cost ~64 cycles each whatever N is (the 128 x 16 A operand is fetched per instruction),
+// so time per key falls with wider key tiles, which shared memory (query + latent ring) does not allow
+// in one CTA.  Moving query dims between TMEM and shared memory (FA_B200_MLA_QT) changes nothing.
 //
 // Reference behaviour: kernels/v11_mla/mla_attention.cu:104-258 (what is computed), and the intended
 // tensor-core backend kernels/v12_mla_tc/mla_tc_attention.cu:94-139, which validates and then raises.
 
 #include <climits>
+#include <cstdlib>
 
 #include "sm100.cuh"
 
@@ -26,14 +35,12 @@ namespace {
 using namespace sm100;
 
 constexpr int kTcThreads = 192;
-constexpr int kTcBN = 64;
+constexpr int kTcBN = 32;
 constexpr int kTcDQK = 576, kTcDV = 512, kTcDVH = 256;
-constexpr int kTcQT = 256;                    // query dims held in tensor memory
 constexpr int kTcKB = kTcDQK / 64;            // 9 column blocks per latent tile
-constexpr int kTcQB = (kTcDQK - kTcQT) / 64;  // 5 query column blocks in shared memory
-constexpr int kTcLBlk = kTcBN * 128;          // bytes of one [64 keys][64 cols] block
+constexpr int kTcLBlk = kTcBN * 128;          // bytes of one [32 keys][64 cols] block
 constexpr int kTcQBlk = 128 * 128;            // bytes of one [128 rows][64 cols] block
-constexpr int kTcStage = kTcKB * kTcLBlk;     // 73 728
+constexpr int kTcStage = kTcKB * kTcLBlk;     // 36 864
 constexpr int kTcMaxPages = 128;          // block-table entries staged per CTA (shared memory is nearly full)
 constexpr float kTcThreshold = 8.f;
 
@@ -75,14 +82,28 @@ __device__ __forceinline__ void tmem_st32r(uint32_t taddr, const uint32_t (&r)[3
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st16r(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// QT: query dims held in tensor memory (0, 128, 256 or 384); the rest sits in shared memory, and what
+// shared memory is left decides the depth of the latent ring.
+template <int kTcQT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_l, const MlaTcParams p) {
+  constexpr int kTcQB = (kTcDQK - kTcQT) / 64;                              // query column blocks in shared memory
+  constexpr int kTcStages = (226 * 1024 - kTcQB * kTcQBlk) / kTcStage > 4 ? 4 : (226 * 1024 - kTcQB * kTcQBlk) / kTcStage;
+  static_assert(kTcStages >= 2, "latent ring needs two stages");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;                          // [5 blocks][128 rows][64 cols]: query dims 256..575
-  uint8_t* sL = sQ + kTcQB * kTcQBlk;          // [2 stages][9 blocks][64 keys][64 cols]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sL + 2 * kTcStage);
-  enum { Q_FULL = 0, QT_READY = 1, KV_FULL = 2, KV_EMPTY = 4, S_FULL = 6, P_READY = 8, O_DONE = 9, NBARS = 10 };
+  uint8_t* sQ = smem;                          // [kTcQB blocks][128 rows][64 cols]: query dims 384..575
+  uint8_t* sL = sQ + kTcQB * kTcQBlk;          // [4 stages][9 blocks][32 keys][64 cols]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sL + kTcStages * kTcStage);
+  enum { Q_FULL = 0, QT_READY = 1, KV_FULL = 2, KV_EMPTY = 6, S_FULL = 10, P_READY = 12, O_DONE = 13, NBARS = 14 };   // room for 4 stages
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + NBARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   int* s_ticket = const_cast<int*>(reinterpret_cast<volatile int*>(s_tmem + 2));
@@ -114,11 +135,11 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     *s_abort = 0;
     mbar_init(bar(Q_FULL), 1);
     mbar_init(bar(QT_READY), 128);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kTcStages; ++s) {
       mbar_init(bar(KV_FULL + s), 1);
       mbar_init(bar(KV_EMPTY + s), 1);
-      mbar_init(bar(S_FULL + s), 1);
     }
+    for (int s = 0; s < 2; ++s) mbar_init(bar(S_FULL + s), 1);
     mbar_init(bar(P_READY), 128);
     mbar_init(bar(O_DONE), 1);
     fence_barrier_init();
@@ -129,7 +150,8 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     tmem_alloc(smem_u32(s_tmem), 512);
     tmem_relinquish();
   }
-  // block-table slice of this key range (every tile lies inside one page: page_size % 64 == 0)
+  // block-table slice of this key range (every tile lies inside one page: page_size % 64 == 0, ranges start
+  // on multiples of 64)
   const int pg0 = k_begin >> p.page_shift;
   if (n_keys > 0) {
     const int pg1 = (k_end - 1) >> p.page_shift;
@@ -147,18 +169,19 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t tm_o = tmem, tm_s = tmem + 256, tm_q = tmem + 384;
+  const uint32_t tm_o = tmem, tm_s = tmem + 256, tm_q = tmem + 320;
+  (void)tm_q;
   const int64_t qrow0 = (int64_t)b * p.M + m0;          // first query row of this tile in the [B*M, 576] view
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
       // ---------------------------------------------------------------- TMA producer
-      mbar_expect_tx(bar(Q_FULL), kTcQB * kTcQBlk);
+      if (kTcQB > 0) mbar_expect_tx(bar(Q_FULL), kTcQB * kTcQBlk);
       for (int kb = 0; kb < kTcQB; ++kb)
         tma_load_2d(smem_u32(sQ + kb * kTcQBlk), &map_q, kTcQT + kb * 64, (int)qrow0, bar(Q_FULL));
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (j >= 2 && !mbar_wait(bar(KV_EMPTY + s), ((j >> 1) - 1) & 1, s_abort, p.status, TC_ERR_KV_EMPTY)) break;
+        const int s = j % kTcStages;
+        if (j >= kTcStages && !mbar_wait(bar(KV_EMPTY + s), ((j / kTcStages) - 1) & 1, s_abort, p.status, TC_ERR_KV_EMPTY)) break;
         const int key = k_begin + j * kTcBN;
         const int pg = key >> p.page_shift;
         const int tok = s_bt[pg - pg0] * p.page_size + (key - (pg << p.page_shift));
@@ -173,21 +196,21 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       constexpr uint32_t idesc_qk = idesc_f16(128, kTcBN, true, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(128, kTcDVH, true, false, true);
       auto issue_qk = [&](int j) {
-        const uint32_t l_base = smem_u32(sL + (j & 1) * kTcStage);
-        const uint32_t d = tm_s + (uint32_t)(j & 1) * 64;
+        const uint32_t l_base = smem_u32(sL + (j % kTcStages) * kTcStage);
+        const uint32_t d = tm_s + (uint32_t)(j & 1) * kTcBN;
 #pragma unroll
-        for (int k = 0; k < kTcQT / 16; ++k)         // query dims 0..255 from tensor memory
+        for (int k = 0; k < kTcQT / 16; ++k)         // query dims 0..383 from tensor memory
           mma_f16_ts(d, tm_q + k * 8, smem_desc_sw128(l_base + (k >> 2) * kTcLBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
 #pragma unroll
-        for (int k = kTcQT / 16; k < kTcDQK / 16; ++k) {   // query dims 256..575 from shared memory
+        for (int k = kTcQT / 16; k < kTcDQK / 16; ++k) {   // query dims 384..575 from shared memory
           const int kq = k - kTcQT / 16;
           mma_f16_ss(d, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kTcQBlk + (kq & 3) * 32, 16, 1024),
-                     smem_desc_sw128(l_base + (k >> 2) * kTcLBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
+                     smem_desc_sw128(l_base + (k >> 2) * kTcLBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
         }
         mma_commit(bar(S_FULL + (j & 1)));
       };
-      bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, TC_ERR_Q) &&
-                mbar_wait(bar(QT_READY), 0, s_abort, p.status, TC_ERR_QT) &&
+      bool ok = (kTcQB == 0 || mbar_wait(bar(Q_FULL), 0, s_abort, p.status, TC_ERR_Q)) &&
+                (kTcQT == 0 || mbar_wait(bar(QT_READY), 0, s_abort, p.status, TC_ERR_QT)) &&
                 mbar_wait(bar(KV_FULL + 0), 0, s_abort, p.status, TC_ERR_KV_FULL);
       if (ok) {
         tc_fence_after();
@@ -195,7 +218,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
       for (int j = 0; ok && j < n_tiles; ++j) {
         if (j + 1 < n_tiles) {
-          ok = mbar_wait(bar(KV_FULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1, s_abort, p.status, TC_ERR_KV_FULL);
+          ok = mbar_wait(bar(KV_FULL + ((j + 1) % kTcStages)), ((j + 1) / kTcStages) & 1, s_abort, p.status, TC_ERR_KV_FULL);
           if (!ok) break;
           tc_fence_after();
           issue_qk(j + 1);      // S[(j+1)&1] last held P of tile j-1, whose P V was issued before: in order
@@ -203,12 +226,12 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         ok = mbar_wait(bar(P_READY), j & 1, s_abort, p.status, TC_ERR_P_READY);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v_base = smem_u32(sL + (j & 1) * kTcStage) + (uint32_t)dvh * 4 * kTcLBlk;
+        const uint32_t v_base = smem_u32(sL + (j % kTcStages) * kTcStage) + (uint32_t)dvh * 4 * kTcLBlk;
 #pragma unroll
         for (int k = 0; k < kTcBN / 16; ++k)
-          mma_f16_ts(tm_o, tm_s + (uint32_t)(j & 1) * 64 + k * 8, smem_desc_sw128(v_base + k * 2048, kTcLBlk, 1024), idesc_pv,
+          mma_f16_ts(tm_o, tm_s + (uint32_t)(j & 1) * kTcBN + k * 8, smem_desc_sw128(v_base + k * 2048, kTcLBlk, 1024), idesc_pv,
                      (j > 0 || k > 0) ? 1u : 0u);
-        mma_commit(bar(KV_EMPTY + (j & 1)));
+        mma_commit(bar(KV_EMPTY + (j % kTcStages)));
         if (j + 1 == n_tiles) mma_commit(bar(O_DONE));
       }
     }
@@ -225,8 +248,8 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const int tile_limit = min(p.causal ? iq_min + qoff : INT_MAX, k_end - 1);
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-    if (n_tiles > 0) {
-      // query dims 0..255 of this row -> tensor memory, two bf16 per column (zero for padding rows)
+    if (n_tiles > 0 && kTcQT > 0) {
+      // leading query dims of this row -> tensor memory, two bf16 per column (zero for padding rows)
       const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + (qrow0 + row) * kTcDQK);
 #pragma unroll
       for (int c = 0; c < kTcQT / 64; ++c) {
@@ -246,19 +269,18 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       ok = mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, TC_ERR_S_FULL);
       if (!ok) break;
       tc_fence_after();
-      float s[64];
-      const uint32_t ts = tm_s + (uint32_t)(j & 1) * 64 + lane_base;
-      tmem_ld32(ts, *reinterpret_cast<float(*)[32]>(&s[0]));
-      tmem_ld32(ts + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+      float s[kTcBN];
+      const uint32_t ts = tm_s + (uint32_t)(j & 1) * kTcBN + lane_base;
+      tmem_ld32(ts, s);
       tmem_wait_ld();
       const int k0 = k_begin + j * kTcBN;
       if (k0 + kTcBN - 1 > tile_limit) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
+        for (int c = 0; c < kTcBN; ++c)
           if (k0 + c > limit) s[c] = -INFINITY;
         // value rows past the end of the sequence may hold anything: zero them so that 0 * x stays 0
         if (k0 + kTcBN > k_end && row < kTcBN && k0 + row >= k_end) {
-          uint8_t* base = sL + (j & 1) * kTcStage + row * 128;
+          uint8_t* base = sL + (j % kTcStages) * kTcStage + row * 128;
 #pragma unroll
           for (int kb = 0; kb < kTcKB; ++kb) {
             uint4* d = reinterpret_cast<uint4*>(base + kb * kTcLBlk);
@@ -270,7 +292,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
       float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
+      for (int c = 0; c < kTcBN; c += 2) {
         mxa = fmaxf(mxa, s[c]);
         mxb = fmaxf(mxb, s[c + 1]);
       }
@@ -284,7 +306,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
+      for (int c = 0; c < kTcBN; c += 2) {
         s[c] = fast_exp2(fmaf(s[c], p.scale_log2, -m_use));
         s[c + 1] = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_use));
         sum0 += s[c];
@@ -303,10 +325,10 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           tmem_st32(tm_o + lane_base + c * 32, o);
         }
       }
-      uint32_t pk[32];
+      uint32_t pk[kTcBN / 2];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) pk[c] = pack_bf2(s[2 * c], s[2 * c + 1]);
-      tmem_st32r(ts, pk);
+      for (int c = 0; c < kTcBN / 2; ++c) pk[c] = pack_bf2(s[2 * c], s[2 * c + 1]);
+      tmem_st16r(ts, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(P_READY));
@@ -402,6 +424,24 @@ bool mla_tc_applicable(const fa_mla_args* a) {
 size_t mla_tc_workspace_bytes(int n_slots, int M) { return (size_t)n_slots * M * (kTcDV + 2) * 4; }
 size_t mla_tc_counters_len(int B, int M) { return (size_t)B * ((M + 127) / 128) * 2 + 1; }
 
+template <int QT>
+static int launch_qt(const CUtensorMap& tq, const CUtensorMap& tl, const MlaTcParams& p, dim3 grid, cudaStream_t st) {
+  constexpr int QB = (kTcDQK - QT) / 64;
+  constexpr int ST = (226 * 1024 - QB * kTcQBlk) / kTcStage > 4 ? 4 : (226 * 1024 - QB * kTcQBlk) / kTcStage;
+  constexpr int SMEM = QB * kTcQBlk + ST * kTcStage + 1024 + 160 + kTcMaxPages * 4;
+  static_assert(SMEM <= 227 * 1024, "MLA tensor-core tile does not fit shared memory");
+  static int configured_device = -1;
+  int dev = 0;
+  FA_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    FA_CUDA_OK(cudaFuncSetAttribute(mla_tc_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured_device = dev;
+  }
+  mla_tc_kernel<QT><<<grid, kTcThreads, SMEM, st>>>(tq, tl, p);
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
+}
+
 int launch_mla_tc(const fa_mla_args* a, cudaStream_t st) {
   const int M = a->H_q * a->N_q;
   const int row_tiles = (M + 127) / 128;
@@ -439,19 +479,15 @@ int launch_mla_tc(const fa_mla_args* a, cudaStream_t st) {
   p.page_shift = __builtin_ctz((unsigned)a->page_size);
   p.B = a->B; p.H_q = a->H_q; p.N_q = a->N_q; p.M = M; p.n_slots = a->n_slots;
   p.causal = a->causal; p.q_offset = a->q_offset; p.out_dtype = a->out_dtype;
-  constexpr int SMEM = kTcQB * kTcQBlk + 2 * kTcStage + 1024 + 128 + kTcMaxPages * 4;
-  static_assert(SMEM <= 227 * 1024, "MLA tensor-core tile does not fit shared memory");
-  static int configured_device = -1;
-  int dev = 0;
-  FA_CUDA_OK(cudaGetDevice(&dev));
-  if (configured_device != dev) {
-    FA_CUDA_OK(cudaFuncSetAttribute(mla_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    configured_device = dev;
-  }
+  // FA_B200_MLA_QT = 0 / 128 / 256 / 384 query dims in tensor memory (default 384)
+  static const int qt = [] { const char* e = getenv("FA_B200_MLA_QT"); return e ? atoi(e) : 384; }();
   dim3 grid((unsigned)a->n_items, 2u, (unsigned)row_tiles);
-  mla_tc_kernel<<<grid, kTcThreads, SMEM, st>>>(tq, tl, p);
-  FA_CUDA_OK(cudaGetLastError());
-  return FA_OK;
+  switch (qt) {
+    case 0: return launch_qt<0>(tq, tl, p, grid, st);
+    case 128: return launch_qt<128>(tq, tl, p, grid, st);
+    case 256: return launch_qt<256>(tq, tl, p, grid, st);
+    default: return launch_qt<384>(tq, tl, p, grid, st);
+  }
 }
 
 }  // namespace fa
