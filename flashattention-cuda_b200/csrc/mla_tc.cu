@@ -35,12 +35,9 @@ namespace {
 using namespace sm100;
 
 constexpr int kTcThreads = 192;
-constexpr int kTcBN = 32;
 constexpr int kTcDQK = 576, kTcDV = 512, kTcDVH = 256;
 constexpr int kTcKB = kTcDQK / 64;            // 9 column blocks per latent tile
-constexpr int kTcLBlk = kTcBN * 128;          // bytes of one [32 keys][64 cols] block
 constexpr int kTcQBlk = 128 * 128;            // bytes of one [128 rows][64 cols] block
-constexpr int kTcStage = kTcKB * kTcLBlk;     // 36 864
 constexpr int kTcMaxPages = 128;          // block-table entries staged per CTA (shared memory is nearly full)
 constexpr float kTcThreshold = 8.f;
 
@@ -92,10 +89,17 @@ __device__ __forceinline__ void tmem_st16r(uint32_t taddr, const uint32_t (&r)[1
 
 // QT: query dims held in tensor memory (0, 128, 256 or 384); the rest sits in shared memory, and what
 // shared memory is left decides the depth of the latent ring.
-template <int kTcQT>
+template <int kTcQT, int kTcBN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_l, const MlaTcParams p) {
   constexpr int kTcQB = (kTcDQK - kTcQT) / 64;                              // query column blocks in shared memory
+  constexpr int kTcLBlk = kTcBN * 128;                                      // bytes of one [BN keys][64 cols] block
+  constexpr int kTcStage = kTcKB * kTcLBlk;
+  // BN = 32: two score buffers, Q L^T of the next tile is issued before P V of the current one.
+  // BN = 64: one score buffer and a strictly serial tile (Q L^T -> softmax -> P V); only two tiles fit in
+  //          shared memory, and releasing a tile's stage before the next Q L^T starts is what lets the
+  //          load of the tile after that overlap a whole tile of work.
+  constexpr bool kSerial = (kTcBN == 64);
   constexpr int kTcStages = (226 * 1024 - kTcQB * kTcQBlk) / kTcStage > 4 ? 4 : (226 * 1024 - kTcQB * kTcQBlk) / kTcStage;
   static_assert(kTcStages >= 2, "latent ring needs two stages");
   extern __shared__ uint8_t smem_raw[];
@@ -197,7 +201,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       constexpr uint32_t idesc_pv = idesc_f16(128, kTcDVH, true, false, true);
       auto issue_qk = [&](int j) {
         const uint32_t l_base = smem_u32(sL + (j % kTcStages) * kTcStage);
-        const uint32_t d = tm_s + (uint32_t)(j & 1) * kTcBN;
+        const uint32_t d = tm_s + (kSerial ? 0u : (uint32_t)(j & 1) * kTcBN);
 #pragma unroll
         for (int k = 0; k < kTcQT / 16; ++k)         // query dims 0..383 from tensor memory
           mma_f16_ts(d, tm_q + k * 8, smem_desc_sw128(l_base + (k >> 2) * kTcLBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
@@ -207,7 +211,7 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
           mma_f16_ss(d, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kTcQBlk + (kq & 3) * 32, 16, 1024),
                      smem_desc_sw128(l_base + (k >> 2) * kTcLBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
         }
-        mma_commit(bar(S_FULL + (j & 1)));
+        mma_commit(bar(S_FULL + (kSerial ? 0 : (j & 1))));
       };
       bool ok = (kTcQB == 0 || mbar_wait(bar(Q_FULL), 0, s_abort, p.status, TC_ERR_Q)) &&
                 (kTcQT == 0 || mbar_wait(bar(QT_READY), 0, s_abort, p.status, TC_ERR_QT)) &&
@@ -217,22 +221,28 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         issue_qk(0);
       }
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) {
-          ok = mbar_wait(bar(KV_FULL + ((j + 1) % kTcStages)), ((j + 1) / kTcStages) & 1, s_abort, p.status, TC_ERR_KV_FULL);
-          if (!ok) break;
-          tc_fence_after();
-          issue_qk(j + 1);      // S[(j+1)&1] last held P of tile j-1, whose P V was issued before: in order
-        }
+        auto next_qk = [&]() {
+          if (j + 1 < n_tiles) {
+            ok = mbar_wait(bar(KV_FULL + ((j + 1) % kTcStages)), ((j + 1) / kTcStages) & 1, s_abort, p.status, TC_ERR_KV_FULL);
+            if (!ok) return;
+            tc_fence_after();
+            issue_qk(j + 1);      // the score buffer last held P of an earlier tile whose P V was issued before: in order
+          }
+        };
+        if (!kSerial) next_qk();
+        if (!ok) break;
         ok = mbar_wait(bar(P_READY), j & 1, s_abort, p.status, TC_ERR_P_READY);
         if (!ok) break;
         tc_fence_after();
         const uint32_t v_base = smem_u32(sL + (j % kTcStages) * kTcStage) + (uint32_t)dvh * 4 * kTcLBlk;
+        const uint32_t p_tmem = tm_s + (kSerial ? 0u : (uint32_t)(j & 1) * kTcBN);
 #pragma unroll
         for (int k = 0; k < kTcBN / 16; ++k)
-          mma_f16_ts(tm_o, tm_s + (uint32_t)(j & 1) * kTcBN + k * 8, smem_desc_sw128(v_base + k * 2048, kTcLBlk, 1024), idesc_pv,
+          mma_f16_ts(tm_o, p_tmem + k * 8, smem_desc_sw128(v_base + k * 2048, kTcLBlk, 1024), idesc_pv,
                      (j > 0 || k > 0) ? 1u : 0u);
         mma_commit(bar(KV_EMPTY + (j % kTcStages)));
         if (j + 1 == n_tiles) mma_commit(bar(O_DONE));
+        if (kSerial) next_qk();
       }
     }
   }
@@ -266,12 +276,14 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_arrive(bar(QT_READY));
     }
     for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, TC_ERR_S_FULL);
+      ok = kSerial ? mbar_wait(bar(S_FULL), j & 1, s_abort, p.status, TC_ERR_S_FULL)
+                   : mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, TC_ERR_S_FULL);
       if (!ok) break;
       tc_fence_after();
       float s[kTcBN];
-      const uint32_t ts = tm_s + (uint32_t)(j & 1) * kTcBN + lane_base;
-      tmem_ld32(ts, s);
+      const uint32_t ts = tm_s + (kSerial ? 0u : (uint32_t)(j & 1) * kTcBN) + lane_base;
+#pragma unroll
+      for (int c = 0; c < kTcBN / 32; ++c) tmem_ld32(ts + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
       tmem_wait_ld();
       const int k0 = k_begin + j * kTcBN;
       if (k0 + kTcBN - 1 > tile_limit) {
@@ -328,7 +340,8 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       uint32_t pk[kTcBN / 2];
 #pragma unroll
       for (int c = 0; c < kTcBN / 2; ++c) pk[c] = pack_bf2(s[2 * c], s[2 * c + 1]);
-      tmem_st16r(ts, pk);
+      if constexpr (kTcBN == 32) tmem_st16r(ts, *reinterpret_cast<uint32_t(*)[16]>(&pk[0]));
+      else tmem_st32r(ts, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(P_READY));
@@ -424,25 +437,28 @@ bool mla_tc_applicable(const fa_mla_args* a) {
 size_t mla_tc_workspace_bytes(int n_slots, int M) { return (size_t)n_slots * M * (kTcDV + 2) * 4; }
 size_t mla_tc_counters_len(int B, int M) { return (size_t)B * ((M + 127) / 128) * 2 + 1; }
 
-template <int QT>
+template <int QT, int BN>
 static int launch_qt(const CUtensorMap& tq, const CUtensorMap& tl, const MlaTcParams& p, dim3 grid, cudaStream_t st) {
   constexpr int QB = (kTcDQK - QT) / 64;
-  constexpr int ST = (226 * 1024 - QB * kTcQBlk) / kTcStage > 4 ? 4 : (226 * 1024 - QB * kTcQBlk) / kTcStage;
-  constexpr int SMEM = QB * kTcQBlk + ST * kTcStage + 1024 + 160 + kTcMaxPages * 4;
+  constexpr int STAGE = kTcKB * BN * 128;
+  constexpr int ST = (226 * 1024 - QB * kTcQBlk) / STAGE > 4 ? 4 : (226 * 1024 - QB * kTcQBlk) / STAGE;
+  constexpr int SMEM = QB * kTcQBlk + ST * STAGE + 1024 + 160 + kTcMaxPages * 4;
   static_assert(SMEM <= 227 * 1024, "MLA tensor-core tile does not fit shared memory");
   static int configured_device = -1;
   int dev = 0;
   FA_CUDA_OK(cudaGetDevice(&dev));
   if (configured_device != dev) {
-    FA_CUDA_OK(cudaFuncSetAttribute(mla_tc_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    FA_CUDA_OK(cudaFuncSetAttribute(mla_tc_kernel<QT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured_device = dev;
   }
-  mla_tc_kernel<QT><<<grid, kTcThreads, SMEM, st>>>(tq, tl, p);
+  mla_tc_kernel<QT, BN><<<grid, kTcThreads, SMEM, st>>>(tq, tl, p);
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }
 
 int launch_mla_tc(const fa_mla_args* a, cudaStream_t st) {
+  // FA_B200_MLA_BN = 32 (two score buffers, 4-stage ring) or 64 (serial tile, 2-stage ring)
+  static const int bn = [] { const char* e = getenv("FA_B200_MLA_BN"); return (e && atoi(e) == 32) ? 32 : 64; }();
   const int M = a->H_q * a->N_q;
   const int row_tiles = (M + 127) / 128;
   CUtensorMap tq, tl;
@@ -456,7 +472,7 @@ int launch_mla_tc(const fa_mla_args* a, cudaStream_t st) {
   {
     const uint64_t dims[2] = {(uint64_t)kTcDQK, (uint64_t)a->num_blocks * a->page_size};
     const uint64_t strides[1] = {(uint64_t)kTcDQK * 2};
-    const uint32_t box[2] = {64, (uint32_t)kTcBN};
+    const uint32_t box[2] = {64, (uint32_t)bn};
     int rc = encode_tensor_map(&tl, FA_BF16, 2, const_cast<void*>(a->l_pool), dims, strides, box, 1);
     if (rc) return rc;
   }
@@ -479,14 +495,14 @@ int launch_mla_tc(const fa_mla_args* a, cudaStream_t st) {
   p.page_shift = __builtin_ctz((unsigned)a->page_size);
   p.B = a->B; p.H_q = a->H_q; p.N_q = a->N_q; p.M = M; p.n_slots = a->n_slots;
   p.causal = a->causal; p.q_offset = a->q_offset; p.out_dtype = a->out_dtype;
-  // FA_B200_MLA_QT = 0 / 128 / 256 / 384 query dims in tensor memory (default 384)
+  // FA_B200_MLA_QT = 0 / 256 / 384 query dims in tensor memory for the 32-key kernel (default 384)
   static const int qt = [] { const char* e = getenv("FA_B200_MLA_QT"); return e ? atoi(e) : 384; }();
   dim3 grid((unsigned)a->n_items, 2u, (unsigned)row_tiles);
+  if (bn == 64) return launch_qt<384, 64>(tq, tl, p, grid, st);
   switch (qt) {
-    case 0: return launch_qt<0>(tq, tl, p, grid, st);
-    case 128: return launch_qt<128>(tq, tl, p, grid, st);
-    case 256: return launch_qt<256>(tq, tl, p, grid, st);
-    default: return launch_qt<384>(tq, tl, p, grid, st);
+    case 0: return launch_qt<0, 32>(tq, tl, p, grid, st);
+    case 256: return launch_qt<256, 32>(tq, tl, p, grid, st);
+    default: return launch_qt<384, 32>(tq, tl, p, grid, st);
   }
 }
 
