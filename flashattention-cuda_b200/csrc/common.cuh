@@ -122,6 +122,16 @@ __device__ __forceinline__ uint32_t e4m3x2_to_h2(uint32_t x) {
   asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }\n" : "=r"(r) : "r"(x));
   return r;
 }
+// four E4M3 bytes of x -> two half2: lo from bytes 0,1 and hi from bytes 2,3 (the 16-bit halves of the
+// register are named directly, no shift)
+__device__ __forceinline__ void e4m3x4_to_h2x2(uint32_t x, uint32_t& lo, uint32_t& hi) {
+  asm("{ .reg .b16 a, b;\n"
+      "  mov.b32 {a, b}, %2;\n"
+      "  cvt.rn.f16x2.e4m3x2 %0, a;\n"
+      "  cvt.rn.f16x2.e4m3x2 %1, b; }\n"
+      : "=r"(lo), "=r"(hi)
+      : "r"(x));
+}
 // four E2M1-pair bytes of x -> four half2 (byte i -> h[i]; low nibble -> low half)
 __device__ __forceinline__ void e2m1x8_to_h2x4(uint32_t x, uint32_t (&h)[4]) {
   asm("{ .reg .b8 b0, b1, b2, b3;\n"

@@ -304,10 +304,15 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
         for (int kp = 0; kp < NKS / 2; ++kp) {
           uint32_t r[4];
           ldmatrix_x4(r, kbase + swz<KROW>(krow, 2 * kp + csel) * 16);
-          mma_rows<false, R8>(s[0], qf[2 * kp], e4m3x2_to_h2(r[0]), e4m3x2_to_h2(r[0] >> 16));
-          mma_rows<false, R8>(s[0], qf[2 * kp + 1], e4m3x2_to_h2(r[1]), e4m3x2_to_h2(r[1] >> 16));
-          mma_rows<false, R8>(s[1], qf[2 * kp], e4m3x2_to_h2(r[2]), e4m3x2_to_h2(r[2] >> 16));
-          mma_rows<false, R8>(s[1], qf[2 * kp + 1], e4m3x2_to_h2(r[3]), e4m3x2_to_h2(r[3] >> 16));
+          uint32_t lo, hi;
+          e4m3x4_to_h2x2(r[0], lo, hi);
+          mma_rows<false, R8>(s[0], qf[2 * kp], lo, hi);
+          e4m3x4_to_h2x2(r[1], lo, hi);
+          mma_rows<false, R8>(s[0], qf[2 * kp + 1], lo, hi);
+          e4m3x4_to_h2x2(r[2], lo, hi);
+          mma_rows<false, R8>(s[1], qf[2 * kp], lo, hi);
+          e4m3x4_to_h2x2(r[3], lo, hi);
+          mma_rows<false, R8>(s[1], qf[2 * kp + 1], lo, hi);
         }
       } else {
         // NVFP4: one 16-byte chunk = 32 head dims = 2 k-steps; lane-in-quad c owns dims 8c..8c+7 of
@@ -433,11 +438,12 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
           ldmatrix_x4_trans(r, vbase + swz<KROW>(vrow, 2 * jp + csel) * 16);
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const uint32_t x0 = prmt(r[2 * u], 0u, 0x3120u);
-            const uint32_t x1 = prmt(r[2 * u + 1], 0u, 0x3120u);
+            uint32_t e0, o0, e1, o1;      // even / odd head dims of keys 0-7 and of keys 8-15
+            e4m3x4_to_h2x2(prmt(r[2 * u], 0u, 0x3120u), e0, o0);
+            e4m3x4_to_h2x2(prmt(r[2 * u + 1], 0u, 0x3120u), e1, o1);
             const int j = 2 * jp + u;
-            mma_rows<false, R8>(o[2 * j], pa, e4m3x2_to_h2(x0), e4m3x2_to_h2(x1));
-            mma_rows<false, R8>(o[2 * j + 1], pa, e4m3x2_to_h2(x0 >> 16), e4m3x2_to_h2(x1 >> 16));
+            mma_rows<false, R8>(o[2 * j], pa, e0, e1);
+            mma_rows<false, R8>(o[2 * j + 1], pa, o0, o1);
           }
         }
       } else {
