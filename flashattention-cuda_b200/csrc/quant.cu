@@ -213,6 +213,71 @@ __global__ void fake_quant_apply_kernel(const float* __restrict__ x, int64_t row
   }
 }
 
+// ---- KV-cache write path: append T new tokens per sequence to a paged pool, quantising on the way ----------
+// x: [B, H, T, d] (f32 / f16 / bf16).  Token t of sequence b goes to logical position pos[b] + t, i.e. to
+// pool row (block_table[b][p / page] * page + p % page, h).  One warp per (b, t, h) row.
+//   mode 0: store as fp16      mode 1: store as bf16
+//   mode 2: FP8 E4M3 with one fp32 scale per row (amax / 448), scale written to scale_pool[row]
+//   mode 3: NVFP4 with the caller's tensor scale: E4M3 micro-scale per 16 elements + packed E2M1 codes
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ x, const int32_t* __restrict__ pos, const int32_t* __restrict__ bt,
+                                 int B, int H, int Tn, int d, int page, int n_logical, int num_blocks, int mode,
+                                 float tensor_scale, uint8_t* __restrict__ pool, float* __restrict__ scale_pool,
+                                 uint8_t* __restrict__ micro_pool, int* __restrict__ status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)B * H * Tn;
+  for (int64_t row = blockIdx.x * (int64_t)(blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += (int64_t)gridDim.x * (blockDim.x >> 5)) {
+    const int t = (int)(row % Tn);
+    const int h = (int)((row / Tn) % H);
+    const int b = (int)(row / ((int64_t)Tn * H));
+    const int p = pos[b] + t;
+    const int lp = p / page;
+    if (p < 0 || lp >= n_logical) { if (status && lane == 0) atomicOr(status, 2); continue; }
+    const int pb = bt[(int64_t)b * n_logical + lp];
+    if ((unsigned)pb >= (unsigned)num_blocks) { if (status && lane == 0) atomicOr(status, 1); continue; }
+    const int64_t prow = ((int64_t)pb * page + (p - lp * page)) * H + h;     // token-head row of the pool
+    const T* xr = x + row * d;
+    if (mode == 0 || mode == 1) {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(pool) + prow * d;
+      for (int i = lane; i < d; i += 32) {
+        const float v = load_f32(xr, i);
+        if (mode == 0) { __half hv = __float2half_rn(v); dst[i] = *reinterpret_cast<uint16_t*>(&hv); }
+        else { __nv_bfloat16 bv = __float2bfloat16_rn(v); dst[i] = *reinterpret_cast<uint16_t*>(&bv); }
+      }
+    } else if (mode == 2) {
+      float m = 0.f;
+      for (int i = lane; i < d; i += 32) m = fmaxf(m, fabsf(load_f32(xr, i)));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float scale = __fdiv_rn(fmaxf(m, 1e-12f), 448.0f);
+      if (lane == 0) scale_pool[prow] = scale;
+      for (int i = lane; i < d; i += 32) pool[prow * d + i] = f32_to_e4m3_rne(__fdiv_rn(load_f32(xr, i), scale));
+    } else {
+      for (int blk = lane; blk < d / 16; blk += 32) {
+        float v[16];
+        float bmax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          v[i] = load_f32(xr, blk * 16 + i);
+          bmax = fmaxf(bmax, fabsf(v[i]));
+        }
+        bmax = fmaxf(bmax, 1e-12f);
+        const uint8_t mb = f32_to_e4m3_rne(__fdiv_rn(__fdiv_rn(bmax, 6.0f), tensor_scale));
+        micro_pool[prow * (d / 16) + blk] = mb;
+        const float eff = __fmul_rn(e4m3_to_f32(mb), tensor_scale);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          lo |= e2m1_code(__fdiv_rn(v[i], eff)) << (4 * i);
+          hi |= e2m1_code(__fdiv_rn(v[8 + i], eff)) << (4 * i);
+        }
+        reinterpret_cast<uint2*>(pool + prow * (d / 2))[blk] = make_uint2(lo, hi);
+      }
+    }
+  }
+}
+
 inline int grid_for(int64_t work, int threads, int sms) {
   const int64_t blocks = (work + threads - 1) / threads;
   return (int)std::max<int64_t>(1, std::min<int64_t>(blocks, (int64_t)sms * 8));
@@ -336,6 +401,37 @@ extern "C" int fa_fake_quant_e2m1(const float* x, int64_t rows, int d, int granu
   const int g = grid_for(rows * d, 256, sms);
   absmax_axis_kernel<<<g, 256, 0, st>>>(x, rows, d, granularity, amax);
   fake_quant_apply_kernel<<<g, 256, 0, st>>>(x, rows, d, granularity, e4m3_scale, amax, out);
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
+}
+
+extern "C" int fa_kv_append(const void* x, int x_dtype, const int32_t* positions, const int32_t* block_table, int B, int H,
+                            int T, int d, int page_size, int n_logical, int num_blocks, int pool_dtype, float tensor_scale,
+                            void* pool, float* scale_pool, uint8_t* micro_pool, int* status, void* stream) {
+  FA_CHECK_ARG(x && positions && block_table && pool, "fa_kv_append: null pointer");
+  FA_CHECK_ARG(B >= 1 && H >= 1 && T >= 1 && d >= 1 && page_size >= 1 && n_logical >= 1 && num_blocks >= 1, "fa_kv_append: bad sizes");
+  int mode;
+  switch (pool_dtype) {
+    case FA_F16: mode = 0; break;
+    case FA_BF16: mode = 1; break;
+    case FA_E4M3: mode = 2; FA_CHECK_ARG(scale_pool != nullptr, "fa_kv_append: e4m3 pools need the per-token scale pool"); break;
+    case FA_NVFP4:
+      mode = 3;
+      FA_CHECK_ARG(micro_pool != nullptr && d % 16 == 0, "fa_kv_append: nvfp4 pools need the micro-scale pool and d % 16 == 0");
+      FA_CHECK_ARG(tensor_scale > 0.f, "fa_kv_append: nvfp4 pools need the positive tensor scale they were quantised with");
+      break;
+    default: return fail(FA_ERR_INVALID, "fa_kv_append: pool dtype must be f16, bf16, e4m3 or nvfp4");
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int sms = std::max(device_sm_count(), 1);
+  const int g = grid_for((int64_t)B * H * T * 32, 256, sms);
+#define FA_APP(TT) kv_append_kernel<TT><<<g, 256, 0, st>>>((const TT*)x, positions, block_table, B, H, T, d, page_size, n_logical, \
+                                                      num_blocks, mode, tensor_scale, (uint8_t*)pool, scale_pool, micro_pool, status)
+  if (x_dtype == FA_F32) FA_APP(float);
+  else if (x_dtype == FA_F16) FA_APP(__half);
+  else if (x_dtype == FA_BF16) FA_APP(__nv_bfloat16);
+  else return fail(FA_ERR_INVALID, "fa_kv_append: x must be f32/f16/bf16");
+#undef FA_APP
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }

@@ -201,3 +201,38 @@ def build_paged_kv_mla(latent, page_size, *, shuffle=True, seed=None):
     l_pack, l_micro, scale_l = quantize_nvfp4(latent)
     lp, lm, block_table, n_k = build_paged_kv(l_pack, l_micro, page_size, shuffle=shuffle, seed=seed)
     return lp, lm, block_table, n_k, scale_l
+
+
+def append_paged_kv(x, pool, block_table, page_size, positions, *, scale_pool=None, micro_pool=None, tensor_scale=0.0):
+    """Write T new tokens per sequence into a paged pool in place (the step before decode).
+
+    x [B, H, T, d] float; positions int32 [B] = logical position of each sequence's first new token.
+    The pool's dtype selects the conversion: float16 / bfloat16 (cast), uint8 with `scale_pool`
+    (FP8 E4M3, one fp32 scale per token per head, as `quantize_fp8_e4m3_per_token`), uint8 with
+    `micro_pool` and `tensor_scale` (NVFP4 relative to a fixed tensor scale, as `quantize_nvfp4`)."""
+    import ctypes as C
+    lib = _lib.load()
+    x = _src(x)
+    B, H, T, d = x.shape
+    positions = positions.to(device=x.device, dtype=torch.int32).contiguous()
+    _require(pool.is_cuda and pool.is_contiguous() and block_table.dtype == torch.int32, "pool must be contiguous CUDA, block_table int32")
+    if pool.dtype == torch.float16:
+        pd = _lib.FA_F16
+    elif pool.dtype == torch.bfloat16:
+        pd = FA_BF16
+    elif pool.dtype == torch.uint8 and micro_pool is not None:
+        pd = _lib.FA_NVFP4
+    elif pool.dtype == torch.uint8:
+        pd = _lib.FA_E4M3
+        _require(scale_pool is not None, "FP8 pools need scale_pool")
+    else:
+        raise RuntimeError("pool must be float16, bfloat16 or uint8")
+    lib.fa_kv_append.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p] + [C.c_int] * 8 + [C.c_float, C.c_void_p,
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    with torch.cuda.device(x.device):
+        _lib.check(lib.fa_kv_append(x.data_ptr(), _DT[x.dtype], positions.data_ptr(), block_table.data_ptr(), B, H, T, d,
+                                    int(page_size), block_table.shape[1], pool.shape[0], pd, float(tensor_scale), pool.data_ptr(),
+                                    scale_pool.data_ptr() if scale_pool is not None else None,
+                                    micro_pool.data_ptr() if micro_pool is not None else None, None,
+                                    _stream(x.device)), "fa_kv_append")
+    return pool

@@ -125,3 +125,4 @@ dequantize_fp8_e4m3 = _fwd("dequantize_fp8_e4m3")
 quantize_nvfp4 = _fwd("quantize_nvfp4")
 dequantize_nvfp4 = _fwd("dequantize_nvfp4")
 paged_gather = _fwd("paged_gather")
+append_paged_kv = _fwd("append_paged_kv")

@@ -292,6 +292,17 @@ FA_API int fa_paged_gather(const void* pool, void* dense, const int32_t* block_t
 FA_API int fa_fake_quant_e2m1(const float* x, int64_t rows, int d, int granularity, int e4m3_scale, float* out,
                               void* scratch, size_t scratch_bytes, void* stream);
 
+/* KV-cache write path: append T new tokens of every sequence to a paged pool, converting / quantising on the
+ * way (the reference only has whole-tensor offline quantisers, fa_kernels/paged.py:94-170; the formulas are
+ * the same, applied per row).  x: device [B, H, T, d] f32/f16/bf16; positions: device int32[B], logical
+ * position of the first new token; pool_dtype FA_F16 / FA_BF16 (convert), FA_E4M3 (one fp32 scale per token
+ * per head = amax/448 into scale_pool [num_blocks, page, H]), FA_NVFP4 (E2M1 codes + E4M3 micro-scales into
+ * micro_pool [.., H, d/16], relative to the caller's fixed tensor_scale).  status: optional device int, bit 0
+ * = bad block-table entry, bit 1 = position outside the table (the row is skipped). */
+FA_API int fa_kv_append(const void* x, int x_dtype, const int32_t* positions, const int32_t* block_table, int B, int H,
+                        int T, int d, int page_size, int n_logical, int num_blocks, int pool_dtype, float tensor_scale,
+                        void* pool, float* scale_pool, uint8_t* micro_pool, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -176,3 +176,40 @@ def test_recipe_rmse_close_to_reference_numbers():
         assert abs(got - want) <= 0.05 * want + 2e-4, (kw, got, want)
     got, want = fp8_attn_rmse(q.cuda(), k.cuda(), v.cuda()), O.fp8_attn_rmse(q.numpy(), k.numpy(), v.numpy())
     assert abs(got - want) <= 0.05 * want + 2e-4
+
+
+@pytest.mark.parametrize("fmt", ["f16", "e4m3", "nvfp4"])
+def test_append_token_by_token_equals_offline_build(fmt):
+    """Appending tokens step by step (varied step sizes, per-sequence positions) must leave the pools
+    byte-identical to quantising / paging the whole tensor at once."""
+    from fa_kernels import paged as P
+    g = torch.Generator().manual_seed(33)
+    B, H, N, d, page = 3, 2, 100, 128, 16
+    k = torch.randn(B, H, N, d, generator=g)
+    k[..., 9] *= 10.0
+    kc = k.cuda()
+    if fmt == "f16":
+        ref_pool, _, bt, _ = P.build_paged_kv(kc.half(), kc.half(), page, seed=5)
+        pool = torch.zeros_like(ref_pool)
+        extra = {}
+    elif fmt == "e4m3":
+        ref_pool, _, bt, _, ref_scales, _ = P.build_paged_kv_fp8_per_token(kc, kc, page, seed=5)
+        pool = torch.zeros_like(ref_pool)
+        extra = {"scale_pool": torch.zeros_like(ref_scales)}
+    else:
+        ref_pool, ref_micro, _, _, bt, _, sk, _ = P.build_paged_kv_nvfp4(kc, kc, page, seed=5)
+        pool = torch.zeros_like(ref_pool)
+        extra = {"micro_pool": torch.zeros_like(ref_micro), "tensor_scale": sk}
+    pos = 0
+    for step in (1, 1, 7, 16, 33, 42):
+        P.append_paged_kv(kc[:, :, pos:pos + step].contiguous(), pool, bt, page, torch.full((B,), pos, dtype=torch.int32), **extra)
+        pos += step
+    assert pos == N
+    # padding rows of the last page stay zero in both
+    np.testing.assert_array_equal(_np(pool.view(torch.uint8) if pool.dtype != torch.uint8 else pool),
+                                  _np(ref_pool.view(torch.uint8) if ref_pool.dtype != torch.uint8 else ref_pool))
+    if fmt == "e4m3":
+        written = _np(P.paged_gather(extra["scale_pool"].unsqueeze(-1), bt, page, N))
+        np.testing.assert_array_equal(written, _np(P.paged_gather(ref_scales.unsqueeze(-1), bt, page, N)))
+    if fmt == "nvfp4":
+        np.testing.assert_array_equal(_np(extra["micro_pool"]), _np(ref_micro))
