@@ -227,6 +227,122 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_long_decode(args):
+    """Quantised-KV long-context decode (B=4, context 1 048 576, page 64), sharded by KV range: rank r owns the
+    keys of logical pages [r*P/N, (r+1)*P/N) of every sequence in its own pool; one step = local decode +
+    one NCCL all-gather of (O, LSE) + merge on every rank.  Strong scaling: the context is fixed."""
+    import torch.distributed as dist
+    from fa_bench import timing, workloads
+    from fa_kernels import _lib, fp8_attention, nvfp4_attention
+    from fa_kernels.distributed import kv_range_decode, kv_range_shards
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    _lib.load()
+    fmt = "e4m3" if args.workload.endswith("fp8") else "nvfp4"
+    ctx, page = args.ctx, 64
+    kb, ke = kv_range_shards(ctx, page, world)[rank]
+    # every rank draws its own shard of the same distribution (seed 3 + rank); q is common (seed 3)
+    w = workloads.quantised_long_context_decode(device, fmt=fmt, ctx=ke - kb, seed=3 + rank)
+    gq = torch.Generator(device=device).manual_seed(3)
+    q = torch.randn(4, 32, 1, 128, device=device, generator=gq).half()
+    if fmt == "e4m3":
+        fn, before, after = fp8_attention, (w["k_pool"], w["v_pool"], w["block_table"], page), (w["k_scale"], w["v_scale"])
+    else:
+        fn = nvfp4_attention
+        before = (w["k_pool"], w["k_micro"], w["v_pool"], w["v_micro"], w["block_table"], page)
+        after = (w["k_scale"], w["v_scale"])
+
+    def step(qq=q):
+        if world == 1:
+            return fn(qq, *before, ke - kb, *after, out_dtype=torch.float16)
+        return kv_range_decode(fn, qq, before, after, local_n_k=ke - kb, key_begin=kb, out_dtype=torch.float16)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        timing.flush_l2(device)
+        step()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        t0 = time.perf_counter()
+        step_ms = []
+        for _ in range(args.steps):
+            timing.flush_l2(device)
+            barrier()                       # ranks enter the collective step together
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            e1.synchronize()
+            step_ms.append(e0.elapsed_time(e1))
+        barrier()
+        while time.perf_counter() - t0 < 1.0:
+            step()
+        torch.cuda.synchronize(device)
+    ms_per_step = sum(step_ms) / len(step_ms)
+    # the decode kernel alone on this rank (roofline of the dominant kernel)
+    kern = lambda: fn(q, *before, ke - kb, *after, out_dtype=torch.float16)
+    kernel_ms = statistics.median(timing.time_cuda(kern, warmup=2, iters=max(args.steps, 5), device=device))
+    # end to end: q from pinned host memory, output back to the host
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty(q.shape, dtype=torch.float16).pin_memory()
+    e2e_ms = []
+    for i in range(3 + args.steps):
+        timing.flush_l2(device)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        o = step(q_host.to(device, non_blocking=True))
+        out_host.copy_(o, non_blocking=True)
+        e1.record()
+        e1.synchronize()
+        if i >= 3:
+            e2e_ms.append(e0.elapsed_time(e1))
+    e2e_mean = sum(e2e_ms) / len(e2e_ms)
+    stats = torch.tensor([ms_per_step, e2e_mean, float(w["kv_bytes"]), kernel_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        mx, sm = stats.clone(), stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms_per_step, e2e_mean, total_bytes = mx[0].item(), mx[1].item(), sm[2].item()
+    else:
+        total_bytes = float(w["kv_bytes"])
+    if rank == 0:
+        peaks = measured_peaks()
+        achieved = w["kv_bytes"] / (kernel_ms * 1e-3) / 1e9
+        line = dict(METRIC)
+        line.update({
+            "value": total_bytes / (ms_per_step * 1e-3) / 1e9, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 compute over " + fmt + " KV", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": 4, "h_q": 32, "h_kv": 8, "d": 128, "ctx": ctx, "page_size": page,
+                       "sharding": "KV range per GPU, one all-gather of (O, LSE) per step, merge kernel on every rank",
+                       "l2": "flushed between steps"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "algorithmic_bytes": w["kv_bytes"],
+                         "kernel_ms": kernel_ms, "traffic": None},
+            "e2e": {"value": total_bytes / (e2e_mean * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_mean,
+                    "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": args.steps * (1 if world == 1 else 2),
+            "clocks": clocks.result,
+        })
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # DRAM bytes per launch of the decode kernel from the committed ncu capture
 # (profiles/paged_decode_fp16_config3.md), or None until one exists.
 TRAFFIC_BYTES_PER_LAUNCH = 1312048592   # 1.303458 GB read + 8.59 MB written
@@ -273,11 +389,36 @@ def cpu_baseline(w, bounded_s):
                       f"on dense KV (dequantise/gather outside the timing), {secs:.2f} s"}
 
 
+def run_reference_long(args, dev):
+    """CPU arm of the long-context workloads: the reference's GQA oracle on the dequantised keys of a
+    131 072-key slice of one sequence per step (a full 1 M-key expansion does not fit host memory)."""
+    from fa_bench import harness, workloads
+    _use_all_host_threads()
+    fmt = "e4m3" if args.workload.endswith("fp8") else "nvfp4"
+    w = workloads.quantised_long_context_decode(dev, fmt=fmt, ctx=131072, batch=1)
+    harness.cpu_sample(args.workload, w, 1.0)
+    done, secs = 0.0, 0.0
+    for _ in range(args.steps):
+        d_, s_, desc = harness.cpu_sample(args.workload, w, 5.0)
+        done += d_
+        secs += s_
+    value = done / secs / 1e9
+    line = dict(METRIC)
+    line.update({"impl": "reference", "value": value, "n_gpus": args.gpus, "steps": args.steps, "warmup": 1,
+                 "ms_per_step": 1e3 * secs / args.steps, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                 "data": "synthetic", "config": {"workload": args.workload, "ctx": args.ctx},
+                 "cpu_baseline": {"value": value, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port", "sample": desc},
+                 "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0})
+    print(json.dumps(line))
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if torch.cuda.is_available() else torch.device("cpu")
+    if args.workload.startswith("long_decode"):
+        return run_reference_long(args, dev)
     w = build_workload(args.workload, dev, 0)
     for _ in range(max(args.warmup, 1)):
         _cpu_pass(w, 5.0)
@@ -307,10 +448,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="paged_gqa_decode_fp16")
+    ap.add_argument("--workload", default="paged_gqa_decode_fp16",
+                    choices=["paged_gqa_decode_fp16", "long_decode_fp8", "long_decode_nvfp4"])
+    ap.add_argument("--ctx", type=int, default=1048576, help="context length of the long-context workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload.startswith("long_decode"):
+        run_long_decode(args)
     else:
         run_ours(args)
 
