@@ -274,6 +274,29 @@ def run_long_decode(args):
         timing.flush_l2(device)
         step()
     barrier()
+    # One step is three launches (decode, all-gather, merge) of a few hundred microseconds in total, so the
+    # host gaps between them matter: replay the step from a CUDA graph (NCCL collectives can be captured).
+    run_step, graphed = step, False
+    if world > 1 and not args.no_graph:
+        try:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    step()
+            torch.cuda.current_stream(device).wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                graph_out = step()
+            run_step, graphed = graph.replay, True
+        except Exception as exc:           # capture is an optimisation; the eager step is the same work
+            print(f"[bench] CUDA graph capture failed on rank {rank}: {exc}", file=sys.stderr)
+            run_step, graphed = step, False
+        flag = torch.tensor([1 if graphed else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)      # all ranks replay graphs, or none does
+        if flag.item() == 0:
+            run_step, graphed = step, False
+    barrier()
     with ClockSampler(local_rank) as clocks:
         t0 = time.perf_counter()
         step_ms = []
@@ -282,13 +305,13 @@ def run_long_decode(args):
             barrier()                       # ranks enter the collective step together
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            step()
+            run_step()
             e1.record()
             e1.synchronize()
             step_ms.append(e0.elapsed_time(e1))
         barrier()
         while time.perf_counter() - t0 < 1.0:
-            step()
+            run_step()
         torch.cuda.synchronize(device)
     ms_per_step = sum(step_ms) / len(step_ms)
     # the decode kernel alone on this rank (roofline of the dominant kernel)
@@ -328,7 +351,7 @@ def run_long_decode(args):
             "dtype": "f16 compute over " + fmt + " KV", "data": "synthetic",
             "config": {"workload": args.workload, "batch": 4, "h_q": 32, "h_kv": 8, "d": 128, "ctx": ctx, "page_size": page,
                        "sharding": "KV range per GPU, one all-gather of (O, LSE) per step, merge kernel on every rank",
-                       "l2": "flushed between steps"},
+                       "l2": "flushed between steps", "cuda_graph": graphed},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "algorithmic_bytes": w["kv_bytes"],
                          "kernel_ms": kernel_ms, "traffic": None},
@@ -451,6 +474,7 @@ def main():
     ap.add_argument("--workload", default="paged_gqa_decode_fp16",
                     choices=["paged_gqa_decode_fp16", "long_decode_fp8", "long_decode_nvfp4"])
     ap.add_argument("--ctx", type=int, default=1048576, help="context length of the long-context workloads")
+    ap.add_argument("--no-graph", action="store_true", help="do not replay the multi-GPU step from a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
