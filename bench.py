@@ -310,7 +310,15 @@ def run_long_decode(args):
             e1.synchronize()
             step_ms.append(e0.elapsed_time(e1))
         barrier()
-        while time.perf_counter() - t0 < 1.0:
+        # keep the clock sampler running for about a second; the step holds a collective, so every rank
+        # must run the same number of extra steps: rank 0 decides, the others follow
+        extra = torch.tensor([0], dtype=torch.int64, device=device)
+        if rank == 0:
+            left = 1.0 - (time.perf_counter() - t0)
+            extra[0] = min(2000, max(0, int(left / max(1e-4, 1e-3 * sum(step_ms) / len(step_ms)))))
+        if world > 1:
+            dist.broadcast(extra, src=0)
+        for _ in range(int(extra.item())):
             run_step()
         torch.cuda.synchronize(device)
     ms_per_step = sum(step_ms) / len(step_ms)
