@@ -368,10 +368,22 @@ def run_long_decode(args):
             "gpu_launches": args.steps * (1 if world == 1 else 2),
             "clocks": clocks.result,
         })
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # a captured graph holds the communicator's kernels: release it before the group goes away, and do
+        # not let a stuck teardown outlive the measurement
+        if graphed:
+            run_step = step
+            graph.reset()
+            del graph, graph_out
+        torch.cuda.synchronize(device)
         dist.barrier()
+        import threading
+        guard = threading.Timer(30.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
         dist.destroy_process_group()
+        guard.cancel()
 
 
 # DRAM bytes per launch of the decode kernel from the committed ncu capture
