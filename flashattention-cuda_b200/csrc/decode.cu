@@ -19,6 +19,7 @@
 
 #include <algorithm>
 #include <climits>
+#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
@@ -575,26 +576,52 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
   if (s_ticket != it.n_split - 1) return;
   __threadfence();
   if (tid == 0) p.counters[cidx] = 0;   // self-reset for the next launch
-  for (int idx = tid; idx < rows_valid * D; idx += kThreads) {
-    const int row = idx / D, dd = idx - row * D;
+  // One thread per (row, four output columns); the partials of kU ranges are fetched before any is
+  // used, so a merge over n ranges costs about n / kU L2 round trips, with a running maximum.
+  constexpr int D4 = D / 4;
+  constexpr int kU = 8;
+  const int64_t slot_stride = (int64_t)p.H_q * p.N_q;
+  for (int idx = tid; idx < rows_valid * D4; idx += kThreads) {
+    const int row = idx / D4, d4 = idx - row * D4;
     const int m = m0 + row;
     const int iq = m / p.G, g = m - iq * p.G;
     const int64_t hrow = (int64_t)(h_kv * p.G + g) * p.N_q + iq;
-    const int64_t slot_stride = (int64_t)p.H_q * p.N_q;
-    float mstar = -INFINITY;
-    for (int sidx = 0; sidx < it.n_split; ++sidx)
-      mstar = fmaxf(mstar, __ldcg(p.part_lse + (it.slot_base + sidx) * slot_stride + hrow));
-    const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
-    float acc = 0.f, l = 0.f;
-    for (int sidx = 0; sidx < it.n_split; ++sidx) {
-      const int64_t prow = (it.slot_base + sidx) * slot_stride + hrow;
-      const float wgt = __expf(__ldcg(p.part_lse + prow) - m_use);
-      acc += wgt * __ldcg(p.part_o + prow * D + dd);
-      l += wgt;
+    const float* lse_base = p.part_lse + it.slot_base * slot_stride + hrow;
+    const float4* o_base = reinterpret_cast<const float4*>(p.part_o + (it.slot_base * slot_stride + hrow) * D) + d4;
+    float m_run = -INFINITY, l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < it.n_split; s0 += kU) {
+      float ls[kU];
+      float4 ov[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int sidx = min(s0 + u, it.n_split - 1);
+        ls[u] = __ldcg(lse_base + sidx * slot_stride);
+        ov[u] = __ldcg(o_base + sidx * slot_stride * D4);
+        if (s0 + u >= it.n_split) ls[u] = -INFINITY;
+      }
+      float mb = m_run;
+#pragma unroll
+      for (int u = 0; u < kU; ++u) mb = fmaxf(mb, ls[u]);
+      if (mb == -INFINITY) continue;
+      const float resc = __expf(m_run - mb);
+      acc.x *= resc, acc.y *= resc, acc.z *= resc, acc.w *= resc, l *= resc;
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const float wgt = __expf(ls[u] - mb);
+        acc.x += wgt * ov[u].x, acc.y += wgt * ov[u].y, acc.z += wgt * ov[u].z, acc.w += wgt * ov[u].w;
+        l += wgt;
+      }
+      m_run = mb;
     }
+    const float inv = (l > 0.f) ? 1.f / l : 0.f;
     const int64_t orow = (int64_t)b * p.H_q * p.N_q + hrow;
-    store_out_dyn(p.out, p.out_dtype, orow * D + dd, (l > 0.f) ? acc / l : 0.f);
-    if (p.lse && dd == 0) p.lse[orow] = (l > 0.f) ? m_use + __logf(l) : -INFINITY;
+    const int64_t o0 = orow * D + d4 * 4;
+    store_out_dyn(p.out, p.out_dtype, o0 + 0, acc.x * inv);
+    store_out_dyn(p.out, p.out_dtype, o0 + 1, acc.y * inv);
+    store_out_dyn(p.out, p.out_dtype, o0 + 2, acc.z * inv);
+    store_out_dyn(p.out, p.out_dtype, o0 + 3, acc.w * inv);
+    if (p.lse && d4 == 0) p.lse[orow] = (l > 0.f) ? m_run + __logf(l) : -INFINITY;
   }
 }
 
@@ -643,6 +670,14 @@ __global__ void merge_partials_kernel(const float* __restrict__ o_parts, const f
 
 using namespace fa;
 
+static double env_double(const char* name, double dflt) {
+  const char* e = std::getenv(name);
+  if (!e || !*e) return dflt;
+  char* end = nullptr;
+  const double x = std::strtod(e, &end);
+  return end == e ? dflt : x;
+}
+
 extern "C" int fa_decode_plan_max_items(const int32_t* seq_lens_host, int n_k, int B, int page_size) {
   (void)page_size;
   int64_t total = 0;
@@ -665,45 +700,75 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
   }
   // Every range pays a fixed start-up (metadata, block table, pipeline fill; worth ~300 keys), so
   // sequences are cut only when there are fewer (sequence, head, row tile) units than CTA slots (up to
-  // 3 per SM): into ~8 waves of ranges when those stay >= 2048 keys, else ~2 ranges per slot, never
-  // shorter than 256 keys.
+  // 3 per SM).  Equal ranges would end with a partly filled last wave as long as one range, so the
+  // ranges shrink instead (guided scheduling): with `share` = keys per slot under perfect balance, each
+  // sequence gives half of what is left of it to ranges of `share` keys, half of the rest to ranges of
+  // share/2, ... down to a floor of 1024 keys; launched longest first, the short ranges fill the tail.
+  // Every level then holds about slots/2 ranges, so no level spills into a second wave of its own.
+  // (Measured on B200, FP8 KV, B=4, 8 KV heads: 1 Mi-key contexts 1810 -> 1691 us against eight equal
+  // waves, 256 Ki-key contexts 553 -> 453 us.)
   const int64_t max_chunk = (int64_t)(kMaxPages - 1) * page_size / kTN * kTN;
   FA_CHECK_ARG(max_chunk >= kTN, "fa_decode_plan: page_size too small");
-  int64_t chunk;
+  const int64_t slots = (int64_t)num_sms * 3;
+  const int64_t units = (int64_t)B * H_kv * row_tiles;
+  const int64_t work = total * H_kv * row_tiles;      // keys x heads x row tiles
+  auto round_tile = [](int64_t x) { return std::max<int64_t>((x + kTN - 1) / kTN * kTN, kTN); };
+  bool guided = false;
+  int64_t chunk = max_chunk;
   if (chunk_hint > 0) {
     chunk = chunk_hint;
-  } else {
-    const int64_t slots = (int64_t)num_sms * 3;
-    const int64_t units = (int64_t)B * H_kv * row_tiles;
-    const int64_t work = total * H_kv * row_tiles;      // keys x heads x row tiles
-    if (units >= slots) {
-      chunk = max_chunk;
-    } else if (work / (8 * slots) >= 2048) {
-      chunk = work / (8 * slots);                       // long contexts: ~8 waves of ranges, start-up stays < 10 %
-    } else {
-      chunk = std::max<int64_t>((work + 2 * slots - 1) / (2 * slots), 256);
-    }
+  } else if (units < slots) {
+    guided = true;
   }
-  chunk = (chunk + kTN - 1) / kTN * kTN;
-  chunk = std::min(chunk, max_chunk);
+  chunk = std::min(round_tile(chunk), max_chunk);
+
+  static const double first_frac = env_double("FA_B200_PLAN_FIRST", 1.0);
+  static const int64_t floor_keys = (int64_t)env_double("FA_B200_PLAN_FLOOR", 1024.0);
+  static const double level_frac = std::min(std::max(env_double("FA_B200_PLAN_LEVEL", 0.5), 0.1), 0.95);
+  const int64_t share = std::max<int64_t>(work / slots, 1);
+  // small jobs: let the floor fall to 256 keys so that there are still ranges for every slot
+  const int64_t floor_chunk = std::min(std::min(round_tile(floor_keys), std::max<int64_t>(round_tile(share / 2), 256)), max_chunk);
 
   std::vector<fa_decode_item> v;
+  std::vector<int64_t> cuts;
   int slot = 0;
   int max_range = 0;
   for (int b = 0; b < B; ++b) {
     const int len = seq_lens_host ? seq_lens_host[b] : n_k;
-    int ns = (int)std::max<int64_t>((len + chunk - 1) / chunk, 1);
-    int64_t cb = ((len + ns - 1) / ns + kTN - 1) / kTN * kTN;
-    if (cb <= 0) cb = kTN;
-    ns = (int)std::max<int64_t>((len + cb - 1) / cb, 1);
-    for (int s = 0; s < ns; ++s) {
+    cuts.clear();                                       // range boundaries after 0
+    if (!guided) {
+      int ns = (int)std::max<int64_t>((len + chunk - 1) / chunk, 1);
+      const int64_t cb = round_tile((len + ns - 1) / ns);
+      ns = (int)std::max<int64_t>((len + cb - 1) / cb, 1);
+      for (int s2 = 1; s2 <= ns; ++s2) cuts.push_back(std::min<int64_t>((int64_t)s2 * cb, len));
+    } else {
+      int64_t pos = 0;
+      int64_t c = std::min(std::max(round_tile((int64_t)(share * first_frac)), floor_chunk), max_chunk);
+      while (pos < len) {
+        const int64_t rem = len - pos;
+        if (c <= floor_chunk || rem <= floor_chunk) {   // the rest in equal ranges of about the floor
+          const int64_t n = std::max<int64_t>((rem + floor_chunk - 1) / floor_chunk, 1);
+          const int64_t cb = round_tile((rem + n - 1) / n);
+          while (pos < len) { pos = std::min<int64_t>(pos + cb, len); cuts.push_back(pos); }
+          break;
+        }
+        const int64_t n = (int64_t)(rem * level_frac) / c;
+        for (int64_t i = 0; i < n; ++i) { pos += c; cuts.push_back(pos); }
+        c = std::max(round_tile(c / 2), floor_chunk);
+      }
+      if (cuts.empty()) cuts.push_back(len);
+    }
+    const int ns = (int)cuts.size();
+    int64_t begin = 0;
+    for (int s2 = 0; s2 < ns; ++s2) {
       fa_decode_item it{};
       it.b = b;
-      it.k_begin = (int)std::min<int64_t>((int64_t)s * cb, len);
-      it.k_end = (int)std::min<int64_t>((int64_t)(s + 1) * cb, len);
+      it.k_begin = (int)begin;
+      it.k_end = (int)cuts[s2];
       it.slot_base = slot;
       it.n_split = ns;
-      it.split = s;
+      it.split = s2;
+      begin = cuts[s2];
       max_range = std::max(max_range, it.k_end - it.k_begin);
       v.push_back(it);
     }
