@@ -483,6 +483,8 @@ bool mla_tc_applicable(const fa_mla_args* a);
 size_t mla_tc_workspace_bytes(int n_slots, int M);
 size_t mla_tc_counters_len(int B, int M);
 int launch_mla_tc(const fa_mla_args* a, cudaStream_t st);
+// CTA-pair tensor-core path (mla_pair.cu); same applicability and workspace as the path above
+int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStream_t st);
 }  // namespace fa
 
 using namespace fa;
@@ -538,6 +540,10 @@ extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   if (tc_enabled && a->engine_hint != 2 && mla_tc_applicable(a)) {
     if (a->workspace_bytes < mla_tc_workspace_bytes(a->n_slots, M))
       return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, mla_tc_workspace_bytes(a->n_slots, M));
+    // FA_B200_MLA_PAIR=1 selects the CTA-pair kernel (cta_group::2)
+    static const bool pair_enabled = [] { const char* e = getenv("FA_B200_MLA_PAIR"); return e && e[0] == '1'; }();
+    if (pair_enabled)
+      return launch_mla_pair(a, mla_tc_counters_len(a->B, M) - 1, reinterpret_cast<cudaStream_t>(a->stream));
     return launch_mla_tc(a, reinterpret_cast<cudaStream_t>(a->stream));
   }
 

@@ -1,0 +1,554 @@
+// MLA latent decode on a pair of CTAs (thread-block cluster of two, tcgen05 cta_group::2).
+// bf16 latent, DQK = 576, DV = 512, page_size a power of two >= 64.
+//
+// One CTA cannot hold the 128 x 512 fp32 output of 128 heads next to a score tile (it is all of tensor
+// memory), and cutting the value dimension over two independent CTAs makes both compute the scores.  A
+// CTA pair avoids both: with cta_group::2 an M = 128 MMA gives each CTA 64 of the 128 rows, and its
+// accumulator of N columns occupies N/2 TMEM columns (rows in lanes 0..63 hold columns [0, N/2), lanes
+// 64..127 hold [N/2, N)).  Per CTA: O[64 x 512] = 256 columns, S[64 x 128] = 64 columns, and 384 of the
+// 576 query dims as the A operand in TMEM (192 columns, the 64 rows written to both lane halves).
+//
+// Per 128-key tile (both CTAs, one thread of the even CTA issues every MMA for the pair):
+//   S = Q L^T    N = 128 keys: CTA r supplies the latent rows of keys [64 r, 64 r + 64) (nine 64-dim blocks)
+//   softmax      thread (row, key half) = TMEM lane; the two halves of a row meet through shared memory;
+//                lazy-rescaled running maximum; P (bf16) goes to shared memory as the next A operand
+//   O += P L_v   two MMAs of N = 256 value columns; CTA r supplies, for all 128 keys, the value columns
+//                [256 s + 128 r, +128) -- so it also loads those four 64-dim blocks of the peer's keys
+// The descriptors of an MMA are the same numbers in both CTAs, so "keys of CTA r" (score operand) and
+// "key half h" (value operand) need separate copies: 9 + 8 blocks of 8 KB per tile, one buffer each; the
+// score blocks are reloaded while softmax and P V run, the value blocks while the next scores are made.
+//
+// Warps: 0 = TMA producer, 1 = TMEM owner (+ MMA issuer in the even CTA), 2..5 = softmax / epilogue.
+// Every wait is bounded (sm100.cuh); the only unbounded synchronisation is the cluster barrier, which
+// both CTAs always reach.
+//
+// Reference behaviour: kernels/v11_mla/mla_attention.cu:104-258 (what is computed), and the intended
+// tensor-core backend kernels/v12_mla_tc/mla_tc_attention.cu:94-139.
+
+#include <climits>
+#include <cstdlib>
+
+#include "sm100.cuh"
+
+namespace fa {
+namespace {
+
+using namespace sm100;
+
+constexpr int kPThreads = 192;
+constexpr int kPDQK = 576, kPDV = 512;
+constexpr int kPBlk = 64 * 128;               // bytes of one [64 rows][64 bf16] block
+constexpr int kPQT = 384;                     // query dims held in tensor memory
+constexpr int kPQB = (kPDQK - kPQT) / 64;     // query blocks in shared memory
+constexpr int kPMaxPages = 128;
+constexpr float kPThreshold = 8.f;
+
+struct MlaPairParams {
+  const uint16_t* q;
+  const int32_t* block_table;
+  const int32_t* q_offsets;
+  const fa_decode_item* items;
+  void* out;
+  float* lse;
+  float* part_o;     // [n_slots][rows][DV]
+  float* part_lse;   // [n_slots][rows]
+  int32_t* counters; // [B][row_tiles][2]
+  int32_t* status;
+  float scale_log2, scale_l;
+  int n_logical, num_blocks, page_size, page_shift, total_tokens;
+  int B, H_q, N_q, M, n_slots;
+  int causal, q_offset, out_dtype;
+};
+
+enum { P2_ERR_Q = 41, P2_ERR_QT = 42, P2_ERR_X_FULL = 43, P2_ERR_X_EMPTY = 44, P2_ERR_Y_FULL = 45, P2_ERR_Y_EMPTY = 46,
+       P2_ERR_S_FULL = 47, P2_ERR_P_READY = 48, P2_ERR_PV_DONE = 49 };
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile into this CTA's shared memory; the bytes are counted on a barrier of the even CTA.
+__device__ __forceinline__ void tma_pair_2d(uint32_t dst, const CUtensorMap* m, int x, int y, uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar_cluster)
+      : "memory");
+}
+__device__ __forceinline__ void mma2_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+               " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma2_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+               " tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// arrive on the barrier at this offset in both CTAs once every MMA issued so far has completed
+__device__ __forceinline__ void mma2_commit_both(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
+mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_l, const MlaPairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                          // [3 blocks][64 rows][64 cols]: query dims 384..575 of this CTA's rows
+  uint8_t* sP = sQ + kPQB * kPBlk;             // [2 key halves][64 rows][64 keys]
+  uint8_t* sX = sP + 2 * kPBlk;                // [9 dim blocks][64 own keys][64 dims]: score operand
+  uint8_t* sY = sX + 9 * kPBlk;                // [2 key halves][2 value segments][2 blocks][64 keys][64 dims]: value operand
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sY + 8 * kPBlk);
+  enum { Q_FULL = 0, QT_READY, X_FULL, X_EMPTY, Y_FULL, Y_EMPTY, S_FULL, P_READY, PV_DONE, NBARS };
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  int* s_ticket = const_cast<int*>(reinterpret_cast<volatile int*>(s_tmem + 2));
+  float* s_red = reinterpret_cast<float*>(s_tmem + 4);             // [2][128]
+  int32_t* s_bt = reinterpret_cast<int32_t*>(s_red + 256);         // [kPMaxPages]
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                 // 0 = even CTA (issues the MMAs), 1 = its peer
+  const fa_decode_item it = p.items[blockIdx.x >> 1];
+  const int b = it.b;
+  const int rt = blockIdx.y;
+  const int tile_m0 = rt * 128;                            // first row of the pair's 128-row tile
+  const int tile_rows = min(128, p.M - tile_m0);
+  const int m0 = tile_m0 + 64 * (int)rank;                 // first row of this CTA
+  const int rows_valid = max(0, min(64, p.M - m0));
+  const int qoff = p.q_offsets ? p.q_offsets[b] : p.q_offset;
+  const int k_begin = it.k_begin;
+  int k_end = it.k_end;
+  // rows are m = h * N_q + i_q; a row may attend keys <= i_q + q_offset.  Both CTAs must agree on the
+  // number of tiles, so the bound is taken over the pair's rows.
+  int iq_max = 0, iq_min = 0;
+  if (p.causal) {
+    const int last = tile_m0 + tile_rows - 1;
+    iq_max = (last / p.N_q > tile_m0 / p.N_q) ? p.N_q - 1 : last % p.N_q;
+    iq_min = (last / p.N_q > tile_m0 / p.N_q) ? 0 : tile_m0 % p.N_q;
+    k_end = min(k_end, max(iq_max + qoff, -1) + 1);
+  }
+  const int n_keys = max(k_end - k_begin, 0);
+  const int n_tiles = (n_keys + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    mbar_init(bar(Q_FULL), 1);
+    mbar_init(bar(QT_READY), 256);
+    mbar_init(bar(X_FULL), 1);
+    mbar_init(bar(X_EMPTY), 1);
+    mbar_init(bar(Y_FULL), 1);
+    mbar_init(bar(Y_EMPTY), 1);
+    mbar_init(bar(S_FULL), 1);
+    mbar_init(bar(P_READY), 256);
+    mbar_init(bar(PV_DONE), 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_l);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(s_tmem)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  // block-table slice of this key range (every 64-key half lies inside one page)
+  const int pg0 = k_begin >> p.page_shift;
+  if (n_keys > 0) {
+    const int pg1 = (k_end - 1) >> p.page_shift;
+    const int32_t* bt = p.block_table + (int64_t)b * p.n_logical;
+    for (int i = threadIdx.x; i <= pg1 - pg0 && i < kPMaxPages; i += kPThreads) {
+      int pid = (pg0 + i < p.n_logical) ? bt[pg0 + i] : -2;
+      if ((unsigned)pid >= (unsigned)p.num_blocks) {
+        if (p.status) atomicOr(p.status, 1);
+        pid = 0;                     // never follow a bad entry: read block 0 instead and flag it
+      }
+      s_bt[i] = pid;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                // barriers of both CTAs are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t tm_o = tmem, tm_q = tmem + 256, tm_s = tmem + 448;
+  const int64_t qrow0 = (int64_t)b * p.M + m0;          // first query row of this CTA in the [B*M, 576] view
+  // token row of a key in the pool view; keys past the range read the zero fill beyond the tensor
+  auto token_of = [&](int key) {
+    if (key >= k_end) return p.total_tokens;
+    const int pg = key >> p.page_shift;
+    return s_bt[pg - pg0] * p.page_size + (key - (pg << p.page_shift));
+  };
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      // ---------------------------------------------------------------- TMA producer (both CTAs)
+      const uint32_t q_full0 = map_to_cta(bar(Q_FULL), 0), x_full0 = map_to_cta(bar(X_FULL), 0), y_full0 = map_to_cta(bar(Y_FULL), 0);
+      if (rank == 0) mbar_expect_tx(bar(Q_FULL), 2 * kPQB * kPBlk);
+      for (int kb = 0; kb < kPQB; ++kb) tma_pair_2d(smem_u32(sQ + kb * kPBlk), &map_q, kPQT + kb * 64, (int)qrow0, q_full0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int k0 = k_begin + j * 128;
+        if (j > 0 && !mbar_wait(bar(X_EMPTY), (j - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
+        if (rank == 0) mbar_expect_tx(bar(X_FULL), 2 * 9 * kPBlk);
+        const int tok_own = token_of(k0 + 64 * (int)rank);
+        for (int d = 0; d < 9; ++d) tma_pair_2d(smem_u32(sX + d * kPBlk), &map_l, d * 64, tok_own, x_full0);
+        if (j > 0 && !mbar_wait(bar(Y_EMPTY), (j - 1) & 1, s_abort, p.status, P2_ERR_Y_EMPTY)) break;
+        if (rank == 0) mbar_expect_tx(bar(Y_FULL), 2 * 8 * kPBlk);
+        for (int h = 0; h < 2; ++h) {
+          const int tok = token_of(k0 + 64 * h);
+          for (int s = 0; s < 2; ++s)
+            for (int i = 0; i < 2; ++i)
+              tma_pair_2d(smem_u32(sY + (((h * 2 + s) * 2) + i) * kPBlk), &map_l, 64 * (4 * s + 2 * (int)rank + i), tok, y_full0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0 && n_tiles > 0) {
+      // ---------------------------------------------------------------- MMA issuer (even CTA, for the pair)
+      constexpr uint32_t idesc_qk = idesc_f16(128, 128, true, false, false);
+      constexpr uint32_t idesc_pv = idesc_f16(128, 256, true, false, true);
+      bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, P2_ERR_Q) && mbar_wait(bar(QT_READY), 0, s_abort, p.status, P2_ERR_QT);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const bool last = (j + 1 == n_tiles);
+        ok = mbar_wait(bar(X_FULL), j & 1, s_abort, p.status, P2_ERR_X_FULL);
+        // the softmax threads of the last tile clear value rows past the end of the sequence, in both
+        // CTAs: they learn that the tile has landed from the score barrier, so wait for all of it here
+        if (ok && last) ok = mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kPQT / 16; ++k)          // query dims 0..383 from tensor memory
+          mma2_ts(tm_s, tm_q + k * 8, smem_desc_sw128(smem_u32(sX) + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
+#pragma unroll
+        for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // query dims 384..575 from shared memory
+          const int kq = k - kPQT / 16;
+          mma2_ss(tm_s, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kPBlk + (kq & 3) * 32, 16, 1024),
+                  smem_desc_sw128(smem_u32(sX) + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
+        }
+        mma2_commit_both(bar(S_FULL));
+        mma2_commit_both(bar(X_EMPTY));
+        ok = mbar_wait(bar(P_READY), j & 1, s_abort, p.status, P2_ERR_P_READY);
+        if (ok && !last) ok = mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const int h = ks >> 2;
+            mma2_ss(tm_o + 128 * s, smem_desc_sw128(smem_u32(sP) + h * kPBlk + (ks & 3) * 32, 16, 1024),
+                    smem_desc_sw128(smem_u32(sY) + ((h * 2 + s) * 2) * kPBlk + (ks & 3) * 2048, kPBlk, 1024), idesc_pv,
+                    (j > 0 || ks > 0) ? 1u : 0u);
+          }
+        mma2_commit_both(bar(Y_EMPTY));
+        mma2_commit_both(bar(PV_DONE));
+      }
+    }
+  }
+  else {
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int quad = warp & 3;
+    const int L = quad * 32 + lane;                   // TMEM lane of this thread
+    const int row = L & 63;                           // row of this CTA
+    const int g = L >> 6;                             // key half (scores) / column half (output)
+    const int tid_sm = L;                             // index among the 128 softmax threads
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const bool row_ok = row < rows_valid;
+    const int m = m0 + row;
+    const int iq = m % p.N_q;
+    const int limit = min(p.causal ? iq + qoff : INT_MAX, k_end - 1);    // largest key this row may attend
+    const int tile_limit = min(p.causal ? iq_min + qoff : INT_MAX, k_end - 1);
+    const uint32_t qt_ready0 = map_to_cta(bar(QT_READY), 0), p_ready0 = map_to_cta(bar(P_READY), 0);
+    float m_ref = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    if (n_tiles > 0) {
+      // leading query dims of this row -> tensor memory, two bf16 per column, the same row in both lane
+      // halves (zero for padding rows)
+      const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + (qrow0 + row) * kPDQK);
+#pragma unroll
+      for (int c = 0; c < kPQT / 64; ++c) {
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 v = row_ok ? qsrc[c * 8 + i] : make_uint4(0, 0, 0, 0);
+          r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+        }
+        tmem_st32u(tm_q + lane_base + c * 32, r);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_cluster(qt_ready0);
+    }
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = mbar_wait(bar(S_FULL), j & 1, s_abort, p.status, P2_ERR_S_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      float s[64];
+      tmem_ld32(tm_s + lane_base, *reinterpret_cast<float(*)[32]>(&s[0]));
+      tmem_ld32(tm_s + lane_base + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+      tmem_wait_ld();
+      const int k0 = k_begin + j * 128;
+      const int k0h = k0 + 64 * g;
+      if (k0 + 127 > tile_limit) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          if (k0h + c > limit) s[c] = -INFINITY;
+      }
+      float mxa = -INFINITY, mxb = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        mxa = fmaxf(mxa, s[c]);
+        mxb = fmaxf(mxb, s[c + 1]);
+      }
+      float* red = s_red + (j & 1) * 128;
+      red[tid_sm] = fmaxf(mxa, mxb);
+      softmax_bar();
+      const float mx = fmaxf(red[tid_sm], red[tid_sm ^ 64]) * p.scale_log2;
+      const bool raise = (mx > m_ref + kPThreshold) || (m_ref == -INFINITY && mx > -INFINITY);
+      float alpha = 1.f;
+      if (raise) {
+        alpha = fast_exp2(m_ref - mx);
+        m_ref = mx;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 64; c += 2) {
+        s[c] = fast_exp2(fmaf(s[c], p.scale_log2, -m_use));
+        s[c + 1] = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_use));
+        sum0 += s[c];
+        sum1 += s[c + 1];
+      }
+      l_run = l_run * alpha + (sum0 + sum1);
+      // P of the previous tile is still being read, and O still written, until its P V has completed
+      if (j > 0) {
+        ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, raise)) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float o[32];
+            tmem_ld32(tm_o + lane_base + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] *= alpha;
+            tmem_st32(tm_o + lane_base + c * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      // this thread's 64 probabilities -> row `row` of P block g (128 bytes, 16-byte chunks swizzled by row)
+      {
+        uint8_t* prow = sP + g * kPBlk + row * 128;
+#pragma unroll
+        for (int c16 = 0; c16 < 8; ++c16) {
+          uint4 v;
+          v.x = pack_bf2(s[8 * c16 + 0], s[8 * c16 + 1]);
+          v.y = pack_bf2(s[8 * c16 + 2], s[8 * c16 + 3]);
+          v.z = pack_bf2(s[8 * c16 + 4], s[8 * c16 + 5]);
+          v.w = pack_bf2(s[8 * c16 + 6], s[8 * c16 + 7]);
+          *reinterpret_cast<uint4*>(prow + ((c16 ^ (row & 7)) << 4)) = v;
+        }
+      }
+      // value rows past the end of the sequence may hold anything: zero them so that 0 * x stays 0
+      if (k0 + 128 > k_end) {
+        const int blk = tid_sm >> 4;                   // 8 value blocks, 16 threads each
+        const int h = blk >> 2;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int kr = (tid_sm & 15) + 16 * q4;
+          if (k0 + 64 * h + kr >= k_end) {
+            uint4* d = reinterpret_cast<uint4*>(sY + blk * kPBlk + kr * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) d[i] = make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive_cluster(p_ready0);
+    }
+    if (ok && n_tiles > 0) ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
+    // the two key halves of a row add up their sums
+    s_red[tid_sm] = l_run;
+    softmax_bar();
+    const float l_tot = l_run + s_red[tid_sm ^ 64];
+    if (ok) {
+      tc_fence_after();
+      const bool single = (it.n_split == 1);
+      const float inv = (l_tot > 0.f) ? p.scale_l / l_tot : 0.f;
+      const float lse = (l_tot > 0.f) ? (m_ref + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
+      const int h = m / p.N_q;
+      const int64_t orow = ((int64_t)b * p.H_q + h) * p.N_q + iq;      // output is [B, H_q, N_q, DV]
+      const int64_t prow = (int64_t)(it.slot_base + it.split) * p.M + m;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float o[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tm_o + lane_base + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0.f;
+        }
+        if (!row_ok) continue;
+        const int dd = 256 * (c >> 2) + 128 * g + 32 * (c & 3);       // value column of TMEM column 32 c in lane half g
+        if (single) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) store_out_dyn(p.out, p.out_dtype, orow * kPDV + dd + e, o[e] * inv);
+        } else {
+          float4* dst = reinterpret_cast<float4*>(p.part_o + prow * kPDV + dd);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dst[e] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv, o[4 * e + 2] * inv, o[4 * e + 3] * inv);
+        }
+      }
+      if (row_ok && g == 0) {
+        if (single) { if (p.lse) p.lse[orow] = lse; }
+        else p.part_lse[prow] = lse;
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                // nothing of the pair touches the other CTA's barriers or TMEM after this
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+  }
+  if (it.n_split == 1 || *s_abort) return;
+
+  // ---- the last CTA of this (sequence, row tile, row half) merges all key ranges ------------------------
+  __threadfence();
+  __syncthreads();
+  const int cidx = (b * gridDim.y + rt) * 2 + (int)rank;
+  if (threadIdx.x == 0) *s_ticket = atomicAdd(p.counters + cidx, 1);
+  __syncthreads();
+  if (*s_ticket != it.n_split - 1) return;
+  __threadfence();
+  if (threadIdx.x == 0) p.counters[cidx] = 0;
+  constexpr int kU = 8;
+  for (int idx = threadIdx.x; idx < rows_valid * (kPDV / 4); idx += kPThreads) {
+    const int row = idx / (kPDV / 4), d4 = idx - row * (kPDV / 4);
+    const int m = m0 + row;
+    const float* lse_base = p.part_lse + (int64_t)it.slot_base * p.M + m;
+    const float4* o_base = reinterpret_cast<const float4*>(p.part_o + ((int64_t)it.slot_base * p.M + m) * kPDV) + d4;
+    float m_run = -INFINITY, l = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < it.n_split; s0 += kU) {
+      float ls[kU];
+      float4 ov[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int sidx = min(s0 + u, it.n_split - 1);
+        ls[u] = __ldcg(lse_base + (int64_t)sidx * p.M);
+        ov[u] = __ldcg(o_base + (int64_t)sidx * p.M * (kPDV / 4));
+        if (s0 + u >= it.n_split) ls[u] = -INFINITY;
+      }
+      float mb = m_run;
+#pragma unroll
+      for (int u = 0; u < kU; ++u) mb = fmaxf(mb, ls[u]);
+      if (mb == -INFINITY) continue;
+      const float resc = __expf(m_run - mb);
+      acc.x *= resc, acc.y *= resc, acc.z *= resc, acc.w *= resc, l *= resc;
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const float wgt = __expf(ls[u] - mb);
+        acc.x += wgt * ov[u].x, acc.y += wgt * ov[u].y, acc.z += wgt * ov[u].z, acc.w += wgt * ov[u].w;
+        l += wgt;
+      }
+      m_run = mb;
+    }
+    const float inv = (l > 0.f) ? 1.f / l : 0.f;
+    const int h = m / p.N_q, iq = m - h * p.N_q;
+    const int64_t orow = ((int64_t)b * p.H_q + h) * p.N_q + iq;
+    const int64_t o0 = orow * kPDV + d4 * 4;
+    store_out_dyn(p.out, p.out_dtype, o0 + 0, acc.x * inv);
+    store_out_dyn(p.out, p.out_dtype, o0 + 1, acc.y * inv);
+    store_out_dyn(p.out, p.out_dtype, o0 + 2, acc.z * inv);
+    store_out_dyn(p.out, p.out_dtype, o0 + 3, acc.w * inv);
+    if (p.lse && d4 == 0) p.lse[orow] = (l > 0.f) ? m_run + __logf(l) : -INFINITY;
+  }
+}
+
+}  // namespace
+
+// Host side; called by fa_mla_decode_fwd (mla.cu) after validation when the tensor-core path applies.
+int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStream_t st) {
+  const int M = a->H_q * a->N_q;
+  const int row_tiles = (M + 127) / 128;
+  CUtensorMap tq, tl;
+  {
+    const uint64_t dims[2] = {(uint64_t)kPDQK, (uint64_t)a->B * M};
+    const uint64_t strides[1] = {(uint64_t)kPDQK * 2};
+    const uint32_t box[2] = {64, 64};
+    int rc = encode_tensor_map(&tq, FA_BF16, 2, const_cast<void*>(a->q), dims, strides, box, 1);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)kPDQK, (uint64_t)a->num_blocks * a->page_size};
+    const uint64_t strides[1] = {(uint64_t)kPDQK * 2};
+    const uint32_t box[2] = {64, 64};
+    int rc = encode_tensor_map(&tl, FA_BF16, 2, const_cast<void*>(a->l_pool), dims, strides, box, 1);
+    if (rc) return rc;
+  }
+  MlaPairParams p{};
+  p.q = reinterpret_cast<const uint16_t*>(a->q);
+  p.block_table = a->block_table;
+  p.q_offsets = a->q_offsets;
+  p.items = a->items;
+  p.out = a->out;
+  p.lse = a->lse;
+  p.part_o = reinterpret_cast<float*>(a->workspace);
+  p.part_lse = p.part_o + (size_t)a->n_slots * M * kPDV;
+  p.counters = a->counters;
+  p.status = a->counters + counters_status_index;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f * a->l_scale;
+  p.scale_l = a->l_scale;
+  p.n_logical = a->n_logical;
+  p.num_blocks = a->num_blocks;
+  p.page_size = a->page_size;
+  p.page_shift = __builtin_ctz((unsigned)a->page_size);
+  p.total_tokens = a->num_blocks * a->page_size;
+  p.B = a->B; p.H_q = a->H_q; p.N_q = a->N_q; p.M = M; p.n_slots = a->n_slots;
+  p.causal = a->causal; p.q_offset = a->q_offset; p.out_dtype = a->out_dtype;
+  constexpr int SMEM = (kPQB + 2 + 9 + 8) * kPBlk + 128 + 16 + 1024 + kPMaxPages * 4 + 1024;
+  static_assert(SMEM <= 227 * 1024, "MLA pair tile does not fit shared memory");
+  static int configured_device = -1;
+  int dev = 0;
+  FA_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    FA_CUDA_OK(cudaFuncSetAttribute(mla_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    configured_device = dev;
+  }
+  dim3 grid(2u * (unsigned)a->n_items, (unsigned)row_tiles, 1u);
+  mla_pair_kernel<<<grid, kPThreads, SMEM, st>>>(tq, tl, p);
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
+}
+
+}  // namespace fa
