@@ -114,6 +114,13 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[3
 }
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
+#ifdef FA_PAIR_TRACE
+__device__ long long g_pair_trace[3][256][8];
+#define PAIR_TRACE(who, j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 256) g_pair_trace[who][j][slot] = clock64(); } while (0)
+#else
+#define PAIR_TRACE(who, j, slot) do { } while (0)
+#endif
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_l, const MlaPairParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -211,10 +218,12 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int j = 0; j < n_tiles; ++j) {
         const int k0 = k_begin + j * 128;
         if (j > 0 && !mbar_wait(bar(X_EMPTY), (j - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
+        PAIR_TRACE(0, j, 0);
         if (rank == 0) mbar_expect_tx(bar(X_FULL), 2 * 9 * kPBlk);
         const int tok_own = token_of(k0 + 64 * (int)rank);
         for (int d = 0; d < 9; ++d) tma_pair_2d(smem_u32(sX + d * kPBlk), &map_l, d * 64, tok_own, x_full0);
         if (j > 0 && !mbar_wait(bar(Y_EMPTY), (j - 1) & 1, s_abort, p.status, P2_ERR_Y_EMPTY)) break;
+        PAIR_TRACE(0, j, 1);
         if (rank == 0) mbar_expect_tx(bar(Y_FULL), 2 * 8 * kPBlk);
         for (int h = 0; h < 2; ++h) {
           const int tok = token_of(k0 + 64 * h);
@@ -224,6 +233,16 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
     }
+#ifdef FA_PAIR_TRACE
+    if (lane == 1 && rank == 0) {      // when do the loads land?
+      for (int j = 0; j < n_tiles; ++j) {
+        if (!mbar_wait(bar(X_FULL), j & 1, s_abort, p.status, P2_ERR_X_FULL)) break;
+        PAIR_TRACE(0, j, 2);
+        if (!mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL)) break;
+        PAIR_TRACE(0, j, 3);
+      }
+    }
+#endif
   } else if (warp == 1) {
     if (lane == 0 && rank == 0 && n_tiles > 0) {
       // ---------------------------------------------------------------- MMA issuer (even CTA, for the pair)
@@ -237,6 +256,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // CTAs: they learn that the tile has landed from the score barrier, so wait for all of it here
         if (ok && last) ok = mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL);
         if (!ok) break;
+        PAIR_TRACE(1, j, 0);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kPQT / 16; ++k)          // query dims 0..383 from tensor memory
@@ -249,9 +269,12 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         mma2_commit_both(bar(S_FULL));
         mma2_commit_both(bar(X_EMPTY));
+        PAIR_TRACE(1, j, 1);
         ok = mbar_wait(bar(P_READY), j & 1, s_abort, p.status, P2_ERR_P_READY);
+        PAIR_TRACE(1, j, 2);
         if (ok && !last) ok = mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL);
         if (!ok) break;
+        PAIR_TRACE(1, j, 3);
         tc_fence_after();
 #pragma unroll
         for (int s = 0; s < 2; ++s)
@@ -264,6 +287,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         mma2_commit_both(bar(Y_EMPTY));
         mma2_commit_both(bar(PV_DONE));
+        PAIR_TRACE(1, j, 4);
       }
     }
   }
@@ -304,11 +328,13 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int j = 0; j < n_tiles; ++j) {
       ok = mbar_wait(bar(S_FULL), j & 1, s_abort, p.status, P2_ERR_S_FULL);
       if (!ok) break;
+      if (L == 0) PAIR_TRACE(2, j, 0);
       tc_fence_after();
       float s[64];
       tmem_ld32(tm_s + lane_base, *reinterpret_cast<float(*)[32]>(&s[0]));
       tmem_ld32(tm_s + lane_base + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
       tmem_wait_ld();
+      if (L == 0) PAIR_TRACE(2, j, 1);
       const int k0 = k_begin + j * 128;
       const int k0h = k0 + 64 * g;
       if (k0 + 127 > tile_limit) {
@@ -342,11 +368,10 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         sum1 += s[c + 1];
       }
       l_run = l_run * alpha + (sum0 + sum1);
-      // P of the previous tile is still being read, and O still written, until its P V has completed
+      if (L == 0) PAIR_TRACE(2, j, 2);
+      // The MMAs run in issue order and this tile's scores were committed after the previous P V was
+      // issued, so that P V has completed: its P may be overwritten and O is quiet.
       if (j > 0) {
-        ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
-        if (!ok) break;
-        tc_fence_after();
         if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -360,6 +385,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_wait_st();
         }
       }
+      if (L == 0) PAIR_TRACE(2, j, 3);
       // this thread's 64 probabilities -> row `row` of P block g (128 bytes, 16-byte chunks swizzled by row)
       {
         uint8_t* prow = sP + g * kPBlk + row * 128;
@@ -387,9 +413,12 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
+      if (L == 0) PAIR_TRACE(2, j, 5);
       fence_proxy_async();
+      if (L == 0) PAIR_TRACE(2, j, 6);
       tc_fence_before();
       mbar_arrive_cluster(p_ready0);
+      if (L == 0) PAIR_TRACE(2, j, 4);
     }
     if (ok && n_tiles > 0) ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
     // the two key halves of a row add up their sums
@@ -550,5 +579,11 @@ int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStre
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }
+
+#ifdef FA_PAIR_TRACE
+extern "C" __attribute__((visibility("default"))) int fa_debug_pair_trace(long long* dst, int n) {
+  return (int)cudaMemcpyFromSymbol(dst, g_pair_trace, sizeof(long long) * (size_t)n);
+}
+#endif
 
 }  // namespace fa
