@@ -5,20 +5,25 @@
 // memory), and cutting the value dimension over two independent CTAs makes both compute the scores.  A
 // CTA pair avoids both: with cta_group::2 an M = 128 MMA gives each CTA 64 of the 128 rows, and its
 // accumulator of N columns occupies N/2 TMEM columns (rows in lanes 0..63 hold columns [0, N/2), lanes
-// 64..127 hold [N/2, N)).  Per CTA: O[64 x 512] = 256 columns, S[64 x 128] = 64 columns, and 384 of the
-// 576 query dims as the A operand in TMEM (192 columns, the 64 rows written to both lane halves).
+// 64..127 hold [N/2, N)).  Per CTA: O[64 x 512] = 256 columns, two S[64 x 128] of 64 columns, and 256 of
+// the 576 query dims as the A operand in TMEM (128 columns, the 64 rows written to both lane halves).
 //
 // Per 128-key tile (both CTAs, one thread of the even CTA issues every MMA for the pair):
 //   S = Q L^T    N = 128 keys: CTA r supplies the latent rows of keys [64 r, 64 r + 64) (nine 64-dim blocks)
 //   softmax      thread (row, key half) = TMEM lane; the two halves of a row meet through shared memory;
 //                lazy-rescaled running maximum; P (bf16) goes to shared memory as the next A operand
-//   O += P L_v   two MMAs of N = 256 value columns; CTA r supplies, for all 128 keys, the value columns
-//                [256 s + 128 r, +128) -- so it also loads those four 64-dim blocks of the peer's keys
-// The descriptors of an MMA are the same numbers in both CTAs, so "keys of CTA r" (score operand) and
-// "key half h" (value operand) need separate copies: 9 + 8 blocks of 8 KB per tile, one buffer each; the
-// score blocks are reloaded while softmax and P V run, the value blocks while the next scores are made.
+//   O += P L_v   per key half h and value segment s one N = 256 MMA group; CTA r supplies the value
+//                columns [256 s + 128 r, +128) of the 64 keys of half h
+// The descriptors of an MMA are the same numbers in both CTAs.  For its own keys a CTA finds its value
+// columns inside the score operand; for the peer's keys it must hold them at the offsets where the peer
+// holds its own -- which is where this CTA keeps the peer's value columns of its own keys, dead once the
+// scores are done.  So after S of a tile those four blocks are overwritten (a second TMA producer) with
+// this CTA's value columns of the peer's keys: 72 KB of shared memory and 104 KB of loads per tile,
+// two tile buffers, two score buffers, two P buffers.  The MMA thread issues whatever is ready (P V
+// first): scores run up to two tiles ahead of the oldest unfinished P V, so softmax overlaps the MMAs.
 //
-// Warps: 0 = TMA producer, 1 = TMEM owner (+ MMA issuer in the even CTA), 2..5 = softmax / epilogue.
+// Warps: 0 = TMA producer (own keys), 1 = TMEM owner (+ MMA issuer in the even CTA), 2..5 = softmax /
+// epilogue, 6 = TMA producer (peer keys).
 // Every wait is bounded (sm100.cuh); the only unbounded synchronisation is the cluster barrier, which
 // both CTAs always reach.
 //
@@ -35,10 +40,10 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kPThreads = 192;
+constexpr int kPThreads = 224;
 constexpr int kPDQK = 576, kPDV = 512;
 constexpr int kPBlk = 64 * 128;               // bytes of one [64 rows][64 bf16] block
-constexpr int kPQT = 384;                     // query dims held in tensor memory
+constexpr int kPQT = 256;                     // query dims held in tensor memory
 constexpr int kPQB = (kPDQK - kPQT) / 64;     // query blocks in shared memory
 constexpr int kPMaxPages = 128;
 constexpr float kPThreshold = 8.f;
@@ -78,6 +83,16 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+// Arrival on a barrier of the even CTA that orders nothing across CTAs by itself: what the waiting MMA
+// thread then starts reads this CTA's own shared / tensor memory, which the fences before the arrival
+// have already published to this SM's tensor core.
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y) : "memory");
 }
 // TMA tile into this CTA's shared memory; the bytes are counted on a barrier of the even CTA.
 __device__ __forceinline__ void tma_pair_2d(uint32_t dst, const CUtensorMap* m, int x, int y, uint32_t bar_cluster) {
@@ -125,12 +140,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_l, const MlaPairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;                          // [3 blocks][64 rows][64 cols]: query dims 384..575 of this CTA's rows
-  uint8_t* sP = sQ + kPQB * kPBlk;             // [2 key halves][64 rows][64 keys]
-  uint8_t* sX = sP + 2 * kPBlk;                // [9 dim blocks][64 own keys][64 dims]: score operand
-  uint8_t* sY = sX + 9 * kPBlk;                // [2 key halves][2 value segments][2 blocks][64 keys][64 dims]: value operand
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sY + 8 * kPBlk);
-  enum { Q_FULL = 0, QT_READY, X_FULL, X_EMPTY, Y_FULL, Y_EMPTY, S_FULL, P_READY, PV_DONE, NBARS };
+  uint8_t* sQ = smem;                          // [5 blocks][64 rows][64 cols]: query dims 256..575 of this CTA's rows
+  uint8_t* sP = sQ + kPQB * kPBlk;             // [2 tiles][2 key halves][64 rows][64 keys]
+  uint8_t* sT = sP + 4 * kPBlk;                // [2 tiles][9 dim blocks][64 keys][64 dims]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sT + 18 * kPBlk);
+  enum { Q_FULL = 0, QT_READY = 1, X_FULL = 2, R_FULL = 4, S_FULL = 6, T_FREE = 8, P_READY = 10, Z_GO = 12, NBARS = 13 };
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   int* s_ticket = const_cast<int*>(reinterpret_cast<volatile int*>(s_tmem + 2));
@@ -161,18 +175,20 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
   const int n_keys = max(k_end - k_begin, 0);
   const int n_tiles = (n_keys + 127) / 128;
+  const bool ragged_end = (n_keys & 127) != 0;             // the last tile has value rows past the sequence
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
     mbar_init(bar(Q_FULL), 1);
     mbar_init(bar(QT_READY), 256);
-    mbar_init(bar(X_FULL), 1);
-    mbar_init(bar(X_EMPTY), 1);
-    mbar_init(bar(Y_FULL), 1);
-    mbar_init(bar(Y_EMPTY), 1);
-    mbar_init(bar(S_FULL), 1);
-    mbar_init(bar(P_READY), 256);
-    mbar_init(bar(PV_DONE), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(X_FULL + i), 1);
+      mbar_init(bar(R_FULL + i), 1);
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(T_FREE + i), 1);
+      mbar_init(bar(P_READY + i), 256);
+    }
+    mbar_init(bar(Z_GO), 1);
     fence_barrier_init();
     tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_l);
@@ -200,7 +216,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   cluster_sync_all();                // barriers of both CTAs are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t tm_o = tmem, tm_q = tmem + 256, tm_s = tmem + 448;
+  const uint32_t tm_o = tmem, tm_q = tmem + 256, tm_s = tmem + 384;     // S of tile j at tm_s + 64 (j & 1)
   const int64_t qrow0 = (int64_t)b * p.M + m0;          // first query row of this CTA in the [B*M, 576] view
   // token row of a key in the pool view; keys past the range read the zero fill beyond the tensor
   auto token_of = [&](int key) {
@@ -211,83 +227,132 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
-      // ---------------------------------------------------------------- TMA producer (both CTAs)
-      const uint32_t q_full0 = map_to_cta(bar(Q_FULL), 0), x_full0 = map_to_cta(bar(X_FULL), 0), y_full0 = map_to_cta(bar(Y_FULL), 0);
+      // ------------------------------------------------- TMA producer of the score operand (both CTAs)
+      // tile j -> buffer j & 1: the nine 64-dim blocks of this CTA's own 64 keys
+      const uint32_t q_full0 = map_to_cta(bar(Q_FULL), 0);
       if (rank == 0) mbar_expect_tx(bar(Q_FULL), 2 * kPQB * kPBlk);
       for (int kb = 0; kb < kPQB; ++kb) tma_pair_2d(smem_u32(sQ + kb * kPBlk), &map_q, kPQT + kb * 64, (int)qrow0, q_full0);
       for (int j = 0; j < n_tiles; ++j) {
-        const int k0 = k_begin + j * 128;
-        if (j > 0 && !mbar_wait(bar(X_EMPTY), (j - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
+        const int bf = j & 1;
+        if (j >= 2 && !mbar_wait(bar(T_FREE + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
         PAIR_TRACE(0, j, 0);
-        if (rank == 0) mbar_expect_tx(bar(X_FULL), 2 * 9 * kPBlk);
-        const int tok_own = token_of(k0 + 64 * (int)rank);
-        for (int d = 0; d < 9; ++d) tma_pair_2d(smem_u32(sX + d * kPBlk), &map_l, d * 64, tok_own, x_full0);
-        if (j > 0 && !mbar_wait(bar(Y_EMPTY), (j - 1) & 1, s_abort, p.status, P2_ERR_Y_EMPTY)) break;
-        PAIR_TRACE(0, j, 1);
-        if (rank == 0) mbar_expect_tx(bar(Y_FULL), 2 * 8 * kPBlk);
-        for (int h = 0; h < 2; ++h) {
-          const int tok = token_of(k0 + 64 * h);
-          for (int s = 0; s < 2; ++s)
-            for (int i = 0; i < 2; ++i)
-              tma_pair_2d(smem_u32(sY + (((h * 2 + s) * 2) + i) * kPBlk), &map_l, 64 * (4 * s + 2 * (int)rank + i), tok, y_full0);
+        const uint32_t x_full0 = map_to_cta(bar(X_FULL + bf), 0);
+        if (rank == 0) mbar_expect_tx(bar(X_FULL + bf), 2 * 9 * kPBlk);
+        const int tok_own = token_of(k_begin + j * 128 + 64 * (int)rank);
+        for (int d = 0; d < 9; ++d) tma_pair_2d(smem_u32(sT + (bf * 9 + d) * kPBlk), &map_l, d * 64, tok_own, x_full0);
+        // pull the tile after the next one into L2 while there is no buffer for it yet
+        if (j + 2 < n_tiles) {
+          const int tok_pf = token_of(k_begin + (j + 2) * 128 + 64 * (int)rank);
+          if (tok_pf < p.total_tokens)
+            for (int d = 0; d < 9; ++d) tma_prefetch_l2_2d(&map_l, d * 64, tok_pf);
         }
       }
     }
 #ifdef FA_PAIR_TRACE
     if (lane == 1 && rank == 0) {      // when do the loads land?
       for (int j = 0; j < n_tiles; ++j) {
-        if (!mbar_wait(bar(X_FULL), j & 1, s_abort, p.status, P2_ERR_X_FULL)) break;
+        if (!mbar_wait(bar(X_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL)) break;
         PAIR_TRACE(0, j, 2);
-        if (!mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL)) break;
+        if (!mbar_wait(bar(R_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, P2_ERR_Y_FULL)) break;
         PAIR_TRACE(0, j, 3);
       }
     }
 #endif
+  } else if (warp == 6) {
+    if (lane == 0 && n_tiles > 0) {
+      // ------------------------------------------------- TMA producer of the peer's keys (both CTAs)
+      // Once the scores of tile j are done, the four blocks of the other CTA's value columns are dead
+      // here: they are overwritten by this CTA's value columns of the peer's 64 keys, which puts the value
+      // operand of key half h at the same offsets in both CTAs.
+      for (int j = 0; j < n_tiles; ++j) {
+        const int bf = j & 1;
+        if (!mbar_wait(bar(S_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_S_FULL)) break;
+        PAIR_TRACE(0, j, 1);
+        const uint32_t r_full0 = map_to_cta(bar(R_FULL + bf), 0);
+        if (rank == 0) mbar_expect_tx(bar(R_FULL + bf), 2 * 4 * kPBlk);
+        const int tok_peer = token_of(k_begin + j * 128 + 64 * (1 - (int)rank));
+        for (int s = 0; s < 2; ++s)
+          for (int i = 0; i < 2; ++i)
+            tma_pair_2d(smem_u32(sT + (bf * 9 + 4 * s + 2 * (1 - (int)rank) + i) * kPBlk), &map_l, 64 * (4 * s + 2 * (int)rank + i), tok_peer,
+                        r_full0);
+      }
+    }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0 && n_tiles > 0) {
-      // ---------------------------------------------------------------- MMA issuer (even CTA, for the pair)
+      // ------------------------------------------------- MMA issuer (even CTA, for the pair)
+      // Scores of up to two tiles ahead of the oldest unfinished P V; whichever is ready is issued, P V first.
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, true, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(128, 256, true, false, true);
       bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, P2_ERR_Q) && mbar_wait(bar(QT_READY), 0, s_abort, p.status, P2_ERR_QT);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const bool last = (j + 1 == n_tiles);
-        ok = mbar_wait(bar(X_FULL), j & 1, s_abort, p.status, P2_ERR_X_FULL);
-        // the softmax threads of the last tile clear value rows past the end of the sequence, in both
-        // CTAs: they learn that the tile has landed from the score barrier, so wait for all of it here
-        if (ok && last) ok = mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL);
-        if (!ok) break;
-        PAIR_TRACE(1, j, 0);
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < kPQT / 16; ++k)          // query dims 0..383 from tensor memory
-          mma2_ts(tm_s, tm_q + k * 8, smem_desc_sw128(smem_u32(sX) + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
-#pragma unroll
-        for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // query dims 384..575 from shared memory
-          const int kq = k - kPQT / 16;
-          mma2_ss(tm_s, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kPBlk + (kq & 3) * 32, 16, 1024),
-                  smem_desc_sw128(smem_u32(sX) + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
-        }
-        mma2_commit_both(bar(S_FULL));
-        mma2_commit_both(bar(X_EMPTY));
-        PAIR_TRACE(1, j, 1);
-        ok = mbar_wait(bar(P_READY), j & 1, s_abort, p.status, P2_ERR_P_READY);
-        PAIR_TRACE(1, j, 2);
-        if (ok && !last) ok = mbar_wait(bar(Y_FULL), j & 1, s_abort, p.status, P2_ERR_Y_FULL);
-        if (!ok) break;
-        PAIR_TRACE(1, j, 3);
-        tc_fence_after();
-#pragma unroll
-        for (int s = 0; s < 2; ++s)
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const int h = ks >> 2;
-            mma2_ss(tm_o + 128 * s, smem_desc_sw128(smem_u32(sP) + h * kPBlk + (ks & 3) * 32, 16, 1024),
-                    smem_desc_sw128(smem_u32(sY) + ((h * 2 + s) * 2) * kPBlk + (ks & 3) * 2048, kPBlk, 1024), idesc_pv,
-                    (j > 0 || ks > 0) ? 1u : 0u);
+      int next_qk = 0, next_pv = 0;
+      bool z_sent = false;
+      long long idle_since = 0;
+      while (ok && next_pv < n_tiles) {
+        bool issued = false;
+        if (next_pv < next_qk) {
+          const int j = next_pv, bf = j & 1;
+          const bool last = (j + 1 == n_tiles);
+          bool ready = mbar_try_wait(bar(R_FULL + bf), (j >> 1) & 1);
+          if (ready && last && ragged_end && !z_sent) {
+            // everything of the last tile has landed in both CTAs: let the softmax threads clear the
+            // value rows past the end of the sequence
+            mbar_arrive(bar(Z_GO));
+            mbar_arrive_cluster(map_to_cta(bar(Z_GO), 1));
+            z_sent = true;
           }
-        mma2_commit_both(bar(Y_EMPTY));
-        mma2_commit_both(bar(PV_DONE));
-        PAIR_TRACE(1, j, 4);
+          ready = ready && mbar_try_wait(bar(P_READY + bf), (j >> 1) & 1);
+          if (ready) {
+            PAIR_TRACE(1, j, 3);
+            tc_fence_after();
+            const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), p_base = smem_u32(sP + bf * 2 * kPBlk);
+#pragma unroll
+            for (int s = 0; s < 2; ++s)
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks) {
+                const int h = ks >> 2;
+                mma2_ss(tm_o + 128 * s, smem_desc_sw128(p_base + h * kPBlk + (ks & 3) * 32, 16, 1024),
+                        smem_desc_sw128(t_base + (4 * s + 2 * h) * kPBlk + (ks & 3) * 2048, kPBlk, 1024), idesc_pv,
+                        (j > 0 || ks > 0) ? 1u : 0u);
+              }
+            mma2_commit_both(bar(T_FREE + bf));
+            PAIR_TRACE(1, j, 4);
+            ++next_pv;
+            issued = true;
+          }
+        }
+        if (!issued && next_qk < n_tiles && next_qk < next_pv + 2) {
+          const int j = next_qk, bf = j & 1;
+          if (mbar_try_wait(bar(X_FULL + bf), (j >> 1) & 1)) {
+            PAIR_TRACE(1, j, 0);
+            tc_fence_after();
+            const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), d_s = tm_s + 64 * bf;
+#pragma unroll
+            for (int k = 0; k < kPQT / 16; ++k)          // leading query dims from tensor memory
+              mma2_ts(d_s, tm_q + k * 8, smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
+#pragma unroll
+            for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // the other query dims from shared memory
+              const int kq = k - kPQT / 16;
+              mma2_ss(d_s, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kPBlk + (kq & 3) * 32, 16, 1024),
+                      smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
+            }
+            mma2_commit_both(bar(S_FULL + bf));
+            PAIR_TRACE(1, j, 1);
+            ++next_qk;
+            issued = true;
+          }
+        }
+        if (issued) {
+          idle_since = 0;
+        } else {
+          if (*s_abort) break;
+          const long long now = clock64();
+          if (idle_since == 0) idle_since = now;
+          else if (now - idle_since > kWaitCycles) {
+            *s_abort = 1;
+            if (p.status) atomicCAS(p.status, 0, P2_ERR_P_READY);
+            break;
+          }
+        }
       }
     }
   }
@@ -304,7 +369,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int iq = m % p.N_q;
     const int limit = min(p.causal ? iq + qoff : INT_MAX, k_end - 1);    // largest key this row may attend
     const int tile_limit = min(p.causal ? iq_min + qoff : INT_MAX, k_end - 1);
-    const uint32_t qt_ready0 = map_to_cta(bar(QT_READY), 0), p_ready0 = map_to_cta(bar(P_READY), 0);
+    const uint32_t qt_ready0 = map_to_cta(bar(QT_READY), 0);
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
     if (n_tiles > 0) {
@@ -323,16 +388,17 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive_cluster(qt_ready0);
+      mbar_arrive_peer(qt_ready0);
     }
     for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(bar(S_FULL), j & 1, s_abort, p.status, P2_ERR_S_FULL);
+      const int bf = j & 1;
+      ok = mbar_wait(bar(S_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_S_FULL);
       if (!ok) break;
       if (L == 0) PAIR_TRACE(2, j, 0);
       tc_fence_after();
       float s[64];
-      tmem_ld32(tm_s + lane_base, *reinterpret_cast<float(*)[32]>(&s[0]));
-      tmem_ld32(tm_s + lane_base + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+      tmem_ld32(tm_s + 64 * bf + lane_base, *reinterpret_cast<float(*)[32]>(&s[0]));
+      tmem_ld32(tm_s + 64 * bf + lane_base + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
       tmem_wait_ld();
       if (L == 0) PAIR_TRACE(2, j, 1);
       const int k0 = k_begin + j * 128;
@@ -369,26 +435,27 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       l_run = l_run * alpha + (sum0 + sum1);
       if (L == 0) PAIR_TRACE(2, j, 2);
-      // The MMAs run in issue order and this tile's scores were committed after the previous P V was
-      // issued, so that P V has completed: its P may be overwritten and O is quiet.
-      if (j > 0) {
-        if (__any_sync(0xffffffffu, raise)) {
+      // O may only be rescaled between two P V: this tile's is not issued before P arrives, the previous
+      // one has to be waited for (rare: the maximum seldom rises by 2^8 after the first tiles)
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        ok = mbar_wait(bar(T_FREE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            float o[32];
-            tmem_ld32(tm_o + lane_base + c * 32, o);
-            tmem_wait_ld();
+        for (int c = 0; c < 8; ++c) {
+          float o[32];
+          tmem_ld32(tm_o + lane_base + c * 32, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] *= alpha;
-            tmem_st32(tm_o + lane_base + c * 32, o);
-          }
-          tmem_wait_st();
+          for (int e = 0; e < 32; ++e) o[e] *= alpha;
+          tmem_st32(tm_o + lane_base + c * 32, o);
         }
+        tmem_wait_st();
       }
       if (L == 0) PAIR_TRACE(2, j, 3);
       // this thread's 64 probabilities -> row `row` of P block g (128 bytes, 16-byte chunks swizzled by row)
       {
-        uint8_t* prow = sP + g * kPBlk + row * 128;
+        uint8_t* prow = sP + (bf * 2 + g) * kPBlk + row * 128;
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16) {
           uint4 v;
@@ -399,15 +466,18 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           *reinterpret_cast<uint4*>(prow + ((c16 ^ (row & 7)) << 4)) = v;
         }
       }
-      // value rows past the end of the sequence may hold anything: zero them so that 0 * x stays 0
-      if (k0 + 128 > k_end) {
+      // value rows past the end of the sequence may hold anything: zero them so that 0 * x stays 0.
+      // Block d of the tile holds keys of half (d >> 1) & 1 in both CTAs once the peer's keys are in.
+      if (ragged_end && j + 1 == n_tiles) {
+        ok = mbar_wait(bar(Z_GO), 0, s_abort, p.status, P2_ERR_Y_FULL);
+        if (!ok) break;
         const int blk = tid_sm >> 4;                   // 8 value blocks, 16 threads each
-        const int h = blk >> 2;
+        const int h = (blk >> 1) & 1;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int kr = (tid_sm & 15) + 16 * q4;
           if (k0 + 64 * h + kr >= k_end) {
-            uint4* d = reinterpret_cast<uint4*>(sY + blk * kPBlk + kr * 128);
+            uint4* d = reinterpret_cast<uint4*>(sT + (bf * 9 + blk) * kPBlk + kr * 128);
 #pragma unroll
             for (int i = 0; i < 8; ++i) d[i] = make_uint4(0, 0, 0, 0);
           }
@@ -417,10 +487,11 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       fence_proxy_async();
       if (L == 0) PAIR_TRACE(2, j, 6);
       tc_fence_before();
-      mbar_arrive_cluster(p_ready0);
+      mbar_arrive_peer(map_to_cta(bar(P_READY + bf), 0));
       if (L == 0) PAIR_TRACE(2, j, 4);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
+    if (ok && n_tiles > 0)
+      ok = mbar_wait(bar(T_FREE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
     // the two key halves of a row add up their sums
     s_red[tid_sm] = l_run;
     softmax_bar();
@@ -565,7 +636,7 @@ int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStre
   p.total_tokens = a->num_blocks * a->page_size;
   p.B = a->B; p.H_q = a->H_q; p.N_q = a->N_q; p.M = M; p.n_slots = a->n_slots;
   p.causal = a->causal; p.q_offset = a->q_offset; p.out_dtype = a->out_dtype;
-  constexpr int SMEM = (kPQB + 2 + 9 + 8) * kPBlk + 128 + 16 + 1024 + kPMaxPages * 4 + 1024;
+  constexpr int SMEM = (kPQB + 4 + 18) * kPBlk + 128 + 16 + 1024 + kPMaxPages * 4 + 1024;
   static_assert(SMEM <= 227 * 1024, "MLA pair tile does not fit shared memory");
   static int configured_device = -1;
   int dev = 0;
