@@ -540,9 +540,9 @@ extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   if (tc_enabled && a->engine_hint != 2 && mla_tc_applicable(a)) {
     if (a->workspace_bytes < mla_tc_workspace_bytes(a->n_slots, M))
       return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, mla_tc_workspace_bytes(a->n_slots, M));
-    // FA_B200_MLA_PAIR=1 selects the CTA-pair kernel (cta_group::2)
-    static const bool pair_enabled = [] { const char* e = getenv("FA_B200_MLA_PAIR"); return e && e[0] == '1'; }();
-    if (pair_enabled)
+    // the CTA-pair kernel (cta_group::2) unless FA_B200_MLA_PAIR=0 asks for the single-CTA one
+    static const bool pair_enabled = [] { const char* e = getenv("FA_B200_MLA_PAIR"); return !(e && e[0] == '0'); }();
+    if (pair_enabled && a->engine_hint != 3)
       return launch_mla_pair(a, mla_tc_counters_len(a->B, M) - 1, reinterpret_cast<cudaStream_t>(a->stream));
     return launch_mla_tc(a, reinterpret_cast<cudaStream_t>(a->stream));
   }

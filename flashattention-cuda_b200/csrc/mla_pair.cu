@@ -127,6 +127,16 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[3
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// non-blocking poll (try_wait may park the thread for a while when the phase is still open)
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
 #ifdef FA_PAIR_TRACE
@@ -144,8 +154,8 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint8_t* sP = sQ + kPQB * kPBlk;             // [2 tiles][2 key halves][64 rows][64 keys]
   uint8_t* sT = sP + 4 * kPBlk;                // [2 tiles][9 dim blocks][64 keys][64 dims]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sT + 18 * kPBlk);
-  enum { Q_FULL = 0, QT_READY = 1, X_FULL = 2, R_FULL = 4, S_FULL = 6, T_FREE = 8, P_READY = 10, Z_GO = 12, NBARS = 13 };
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 16);
+  enum { Q_FULL = 0, QT_READY = 1, X_FULL = 2, R_FULL = 4, S_FULL = 6, T_FREE = 8, P_READY = 10, Z_GO = 12, X_FULLB = 13, T_FREEA = 15, NBARS = 17 };
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   int* s_ticket = const_cast<int*>(reinterpret_cast<volatile int*>(s_tmem + 2));
   float* s_red = reinterpret_cast<float*>(s_tmem + 4);             // [2][128]
@@ -183,6 +193,8 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     mbar_init(bar(QT_READY), 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(X_FULL + i), 1);
+      mbar_init(bar(X_FULLB + i), 1);
+      mbar_init(bar(T_FREEA + i), 1);
       mbar_init(bar(R_FULL + i), 1);
       mbar_init(bar(S_FULL + i), 1);
       mbar_init(bar(T_FREE + i), 1);
@@ -234,12 +246,17 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int kb = 0; kb < kPQB; ++kb) tma_pair_2d(smem_u32(sQ + kb * kPBlk), &map_q, kPQT + kb * 64, (int)qrow0, q_full0);
       for (int j = 0; j < n_tiles; ++j) {
         const int bf = j & 1;
-        if (j >= 2 && !mbar_wait(bar(T_FREE + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
-        PAIR_TRACE(0, j, 0);
-        const uint32_t x_full0 = map_to_cta(bar(X_FULL + bf), 0);
-        if (rank == 0) mbar_expect_tx(bar(X_FULL + bf), 2 * 9 * kPBlk);
+        // blocks 0..3 are released by the first half of the P V of the tile that used this buffer, the rest
+        // by the second half; the scores start on blocks 0..3
         const int tok_own = token_of(k_begin + j * 128 + 64 * (int)rank);
-        for (int d = 0; d < 9; ++d) tma_pair_2d(smem_u32(sT + (bf * 9 + d) * kPBlk), &map_l, d * 64, tok_own, x_full0);
+        if (j >= 2 && !mbar_wait(bar(T_FREEA + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
+        PAIR_TRACE(0, j, 0);
+        const uint32_t xa_full0 = map_to_cta(bar(X_FULL + bf), 0), xb_full0 = map_to_cta(bar(X_FULLB + bf), 0);
+        if (rank == 0) mbar_expect_tx(bar(X_FULL + bf), 2 * 4 * kPBlk);
+        for (int d = 0; d < 4; ++d) tma_pair_2d(smem_u32(sT + (bf * 9 + d) * kPBlk), &map_l, d * 64, tok_own, xa_full0);
+        if (j >= 2 && !mbar_wait(bar(T_FREE + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
+        if (rank == 0) mbar_expect_tx(bar(X_FULLB + bf), 2 * 5 * kPBlk);
+        for (int d = 4; d < 9; ++d) tma_pair_2d(smem_u32(sT + (bf * 9 + d) * kPBlk), &map_l, d * 64, tok_own, xb_full0);
         // pull the tile after the next one into L2 while there is no buffer for it yet
         if (j + 2 < n_tiles) {
           const int tok_pf = token_of(k_begin + (j + 2) * 128 + 64 * (int)rank);
@@ -289,24 +306,29 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       long long idle_since = 0;
       while (ok && next_pv < n_tiles) {
         bool issued = false;
-        if (next_pv < next_qk) {
+        // poll the three barriers back to back (each poll is a shared-memory round trip), then decide
+        const bool have_pv = next_pv < next_qk;
+        const bool have_qk = next_qk < n_tiles && next_qk < next_pv + 2;
+        const int pj = next_pv, qj = min(next_qk, n_tiles - 1);
+        const bool r_ok = mbar_test(bar(R_FULL + (pj & 1)), (pj >> 1) & 1);
+        const bool p_ok = mbar_test(bar(P_READY + (pj & 1)), (pj >> 1) & 1);
+        const bool x_ok = mbar_test(bar(X_FULL + (qj & 1)), (qj >> 1) & 1);
+        if (have_pv) {
           const int j = next_pv, bf = j & 1;
           const bool last = (j + 1 == n_tiles);
-          bool ready = mbar_try_wait(bar(R_FULL + bf), (j >> 1) & 1);
-          if (ready && last && ragged_end && !z_sent) {
+          if (r_ok && last && ragged_end && !z_sent) {
             // everything of the last tile has landed in both CTAs: let the softmax threads clear the
             // value rows past the end of the sequence
             mbar_arrive(bar(Z_GO));
             mbar_arrive_cluster(map_to_cta(bar(Z_GO), 1));
             z_sent = true;
           }
-          ready = ready && mbar_try_wait(bar(P_READY + bf), (j >> 1) & 1);
-          if (ready) {
+          if (r_ok && p_ok) {
             PAIR_TRACE(1, j, 3);
             tc_fence_after();
             const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), p_base = smem_u32(sP + bf * 2 * kPBlk);
 #pragma unroll
-            for (int s = 0; s < 2; ++s)
+            for (int s = 0; s < 2; ++s) {
 #pragma unroll
               for (int ks = 0; ks < 8; ++ks) {
                 const int h = ks >> 2;
@@ -314,21 +336,25 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                         smem_desc_sw128(t_base + (4 * s + 2 * h) * kPBlk + (ks & 3) * 2048, kPBlk, 1024), idesc_pv,
                         (j > 0 || ks > 0) ? 1u : 0u);
               }
-            mma2_commit_both(bar(T_FREE + bf));
+              mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
+            }
             PAIR_TRACE(1, j, 4);
             ++next_pv;
             issued = true;
           }
         }
-        if (!issued && next_qk < n_tiles && next_qk < next_pv + 2) {
+        if (!issued && have_qk) {
           const int j = next_qk, bf = j & 1;
-          if (mbar_try_wait(bar(X_FULL + bf), (j >> 1) & 1)) {
+          if (x_ok) {
             PAIR_TRACE(1, j, 0);
             tc_fence_after();
             const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), d_s = tm_s + 64 * bf;
 #pragma unroll
             for (int k = 0; k < kPQT / 16; ++k)          // leading query dims from tensor memory
               mma2_ts(d_s, tm_q + k * 8, smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
+            ok = mbar_wait(bar(X_FULLB + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
             for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // the other query dims from shared memory
               const int kq = k - kPQT / 16;
@@ -652,6 +678,11 @@ int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStre
 }
 
 #ifdef FA_PAIR_TRACE
+extern "C" __attribute__((visibility("default"))) int fa_debug_pair_trace_clear() {
+  void* ptr = nullptr;
+  cudaGetSymbolAddress(&ptr, g_pair_trace);
+  return (int)cudaMemset(ptr, 0, sizeof(g_pair_trace));
+}
 extern "C" __attribute__((visibility("default"))) int fa_debug_pair_trace(long long* dst, int n) {
   return (int)cudaMemcpyFromSymbol(dst, g_pair_trace, sizeof(long long) * (size_t)n);
 }

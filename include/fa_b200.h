@@ -247,8 +247,10 @@ typedef struct fa_mla_args {
   int32_t* counters;
   size_t counters_len;
   void* stream;
-  int engine_hint;   /* 0 = choose; 2 = force the mma.sync kernel (the tcgen05 kernel needs a bf16 (576, 512)
-                        latent, page_size a power of two >= 64 and key ranges <= fa_mla_tc_max_range) */
+  int engine_hint;   /* 0 = choose (tcgen05 on a CTA pair where it applies); 2 = force the mma.sync kernel;
+                        3 = the single-CTA tcgen05 kernel instead of the pair.  The tcgen05 kernels need a
+                        bf16 (576, 512) latent, page_size a power of two >= 64 and key ranges <=
+                        fa_mla_tc_max_range */
 } fa_mla_args;
 FA_API size_t fa_mla_counters_len(int B, int H_q, int N_q);
 FA_API size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV);

@@ -182,15 +182,49 @@ def test_mla_tensor_core_path_matches_oracle_and_legacy_kernel(h_q, page_size):
     scale = 1.0 / 576 ** 0.5
     out, lse = mla_decode(q_t.cuda(), l_pool, None, bt, page_size, lens, 512, 1.0, scale, return_lse=True)
     legacy = mla_decode(q_t.cuda(), l_pool, None, bt, page_size, lens, 512, 1.0, scale, engine_hint=2)
+    single, single_lse = mla_decode(q_t.cuda(), l_pool, None, bt, page_size, lens, 512, 1.0, scale, return_lse=True,
+                                    engine_hint=3)          # the one-CTA tcgen05 kernel
     torch.cuda.synchronize()
-    for b, n in enumerate(lens):
-        if n == 0:
-            assert (out[b] == 0).all() and torch.isneginf(lse[b]).all()
-            continue
-        ref, ref_lse = O.mla_attention_ref(q[b:b + 1], hat[b][None], 512, return_lse=True)
-        assert_close(out[b:b + 1], ref, what=f"mla tc seq {b}")
-        np.testing.assert_allclose(lse[b:b + 1].cpu().numpy(), ref_lse, atol=3e-3, rtol=1e-3)
+    for name, o_, l_ in (("pair", out, lse), ("single", single, single_lse)):
+        for b, n in enumerate(lens):
+            if n == 0:
+                assert (o_[b] == 0).all() and torch.isneginf(l_[b]).all()
+                continue
+            ref, ref_lse = O.mla_attention_ref(q[b:b + 1], hat[b][None], 512, return_lse=True)
+            assert_close(o_[b:b + 1], ref, what=f"mla tc ({name}) seq {b}")
+            np.testing.assert_allclose(l_[b:b + 1].cpu().numpy(), ref_lse, atol=3e-3, rtol=1e-3)
     assert_close(out, legacy.cpu().numpy(), what="tc vs mma.sync")
+
+
+def test_mla_pair_kernel_poisoned_pool_and_multi_query():
+    """The CTA-pair kernel: pool slots the block table does not reference and the tail of the last page
+    hold NaN (they must never reach the output), several query rows per head (rows m = h * N_q + i_q cross
+    the 64-row boundary between the two CTAs), causal with q_offset, ranges split by a chunk hint."""
+    from fa_kernels._mla import mla_decode
+    page_size, h_q, n_q = 64, 48, 3
+    lens = [700, 130, 65, 3000]
+    B = len(lens)
+    q_t, q = randn((B, h_q, n_q, 576), 91, torch.bfloat16)
+    hat, l_pool, bt = _bf16_latent(lens, page_size, 91)
+    l_pool = l_pool.clone()
+    used = torch.zeros(l_pool.shape[0], dtype=torch.bool, device=l_pool.device)
+    for b, n in enumerate(lens):
+        npg = (n + page_size - 1) // page_size
+        pages = bt[b, :npg].long()
+        used[pages] = True
+        if n % page_size:
+            l_pool[pages[-1], n % page_size:] = float("nan")
+    l_pool[~used] = float("nan")
+    scale = 1.0 / 576 ** 0.5
+    for causal, hint in ((False, 0), (True, 0), (True, 512)):
+        q_off = [n - n_q for n in lens]
+        out = mla_decode(q_t.cuda(), l_pool, None, bt, page_size, lens, 512, 1.0, scale, causal=causal,
+                         q_offset=torch.tensor(q_off, dtype=torch.int32) if causal else 0, chunk_hint=hint)
+        torch.cuda.synchronize()
+        assert torch.isfinite(out).all()
+        for b in range(B):
+            ref = O.mla_attention_ref(q[b:b + 1], hat[b][None], 512, causal=causal, q_offset=q_off[b] if causal else 0)
+            assert_close(out[b:b + 1], ref, what=f"mla pair causal={causal} hint={hint} seq {b}")
 
 
 @pytest.mark.parametrize("causal", [False, True])
