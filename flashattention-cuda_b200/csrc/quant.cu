@@ -345,6 +345,64 @@ extern "C" int fa_quantize_nvfp4(const void* x, int x_dtype, int64_t n, uint8_t*
   return FA_OK;
 }
 
+// ---- quantised MLA latent -> bf16 pool (the operand format of the tensor-core MLA kernels) -----------------
+// Only the tokens of the planned key ranges are expanded, each into the same pool row of the bf16 copy.
+// One thread per 16 elements (one NVFP4 micro-block, or 16 E4M3 bytes of a token row); grid (items, 8).
+__global__ void expand_latent_kernel(const uint8_t* __restrict__ src, const uint8_t* __restrict__ micro,
+                                     const float* __restrict__ token_scale, float tensor_scale, int is_nvfp4,
+                                     const int32_t* __restrict__ block_table, int n_logical, int num_blocks, int page_size,
+                                     int page_shift, const fa_decode_item* __restrict__ items, int dqk,
+                                     __nv_bfloat16* __restrict__ out) {
+  const fa_decode_item it = items[blockIdx.x];
+  const int per_tok = dqk / 16;
+  const int64_t n_tok = it.k_end - it.k_begin;
+  const int64_t lo = n_tok * blockIdx.y / gridDim.y, hi = n_tok * (blockIdx.y + 1) / gridDim.y;
+  const int32_t* bt = block_table + (int64_t)it.b * n_logical;
+  for (int64_t w = lo * per_tok + threadIdx.x; w < hi * per_tok; w += blockDim.x) {
+    const int key = it.k_begin + (int)(w / per_tok);
+    const int c16 = (int)(w % per_tok);
+    const int pg = key >> page_shift;
+    const int pid = pg < n_logical ? bt[pg] : -1;
+    if ((unsigned)pid >= (unsigned)num_blocks) continue;          // the attention kernel flags bad entries
+    const int64_t i = ((int64_t)pid * page_size + (key - (pg << page_shift))) * per_tok + c16;   // 16-element chunk in the pool
+    float v[16];
+    if (is_nvfp4) {
+      const uint2 q = *reinterpret_cast<const uint2*>(src + i * 8);
+      const float m = __fmul_rn(e4m3_to_f32(micro[i]), tensor_scale);
+      uint32_t h[8];                                   // sixteen codes -> eight half2 (exact)
+      e2m1x8_to_h2x4(q.x, *reinterpret_cast<uint32_t(*)[4]>(&h[0]));
+      e2m1x8_to_h2x4(q.y, *reinterpret_cast<uint32_t(*)[4]>(&h[4]));
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[e]));
+        v[2 * e] = __fmul_rn(f.x, m);
+        v[2 * e + 1] = __fmul_rn(f.y, m);
+      }
+    } else {
+      const uint4 q = *reinterpret_cast<const uint4*>(src + i * 16);
+      const float sc = token_scale ? token_scale[i / per_tok] : tensor_scale;
+      const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {                    // four bytes -> two half2 (exact, NaN stays NaN)
+        uint32_t lo, hi;
+        e4m3x4_to_h2x2(ws[e], lo, hi);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+        const float2 b2 = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+        v[4 * e] = __fmul_rn(a.x, sc);
+        v[4 * e + 1] = __fmul_rn(a.y, sc);
+        v[4 * e + 2] = __fmul_rn(b2.x, sc);
+        v[4 * e + 3] = __fmul_rn(b2.y, sc);
+      }
+    }
+    uint4 o0, o1;
+    o0.x = pack_bf2(v[0], v[1]);   o0.y = pack_bf2(v[2], v[3]);   o0.z = pack_bf2(v[4], v[5]);   o0.w = pack_bf2(v[6], v[7]);
+    o1.x = pack_bf2(v[8], v[9]);   o1.y = pack_bf2(v[10], v[11]); o1.z = pack_bf2(v[12], v[13]); o1.w = pack_bf2(v[14], v[15]);
+    uint4* dst = reinterpret_cast<uint4*>(out + i * 16);
+    dst[0] = o0;
+    dst[1] = o1;
+  }
+}
+
 extern "C" int fa_dequantize_nvfp4(const uint8_t* packed, const uint8_t* micro, int64_t n, float scale, float* out, void* stream) {
   FA_CHECK_ARG(packed && micro && out && n >= 16 && n % 16 == 0, "fa_dequantize_nvfp4: bad arguments");
   const int sms = std::max(device_sm_count(), 1);
@@ -432,6 +490,22 @@ extern "C" int fa_kv_append(const void* x, int x_dtype, const int32_t* positions
   else if (x_dtype == FA_BF16) FA_APP(__nv_bfloat16);
   else return fail(FA_ERR_INVALID, "fa_kv_append: x must be f32/f16/bf16");
 #undef FA_APP
+  FA_CUDA_OK(cudaGetLastError());
+  return FA_OK;
+}
+
+extern "C" int fa_mla_expand_latent(const void* l_pool, int latent_dtype, const uint8_t* l_micro, const float* token_scale,
+                                    float tensor_scale, const int32_t* block_table, int n_logical, int num_blocks, int page_size,
+                                    const fa_decode_item* items, int n_items, int dqk, void* out_bf16, void* stream) {
+  FA_CHECK_ARG(l_pool && out_bf16 && block_table && items, "fa_mla_expand_latent: null pointer");
+  FA_CHECK_ARG(n_items >= 1 && n_logical >= 1 && num_blocks >= 1 && dqk >= 16 && dqk % 16 == 0, "fa_mla_expand_latent: bad sizes");
+  FA_CHECK_ARG(page_size >= 1 && (page_size & (page_size - 1)) == 0, "fa_mla_expand_latent: page_size must be a power of two");
+  FA_CHECK_ARG(latent_dtype == FA_E4M3 || latent_dtype == FA_NVFP4, "fa_mla_expand_latent: latent must be E4M3 or NVFP4");
+  FA_CHECK_ARG(latent_dtype != FA_NVFP4 || l_micro != nullptr, "fa_mla_expand_latent: NVFP4 needs micro-scales");
+  dim3 grid((unsigned)n_items, 8u, 1u);
+  expand_latent_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint8_t*>(l_pool), l_micro, token_scale, tensor_scale, latent_dtype == FA_NVFP4 ? 1 : 0, block_table,
+      n_logical, num_blocks, page_size, __builtin_ctz((unsigned)page_size), items, dqk, reinterpret_cast<__nv_bfloat16*>(out_bf16));
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }

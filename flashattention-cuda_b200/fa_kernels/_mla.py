@@ -32,6 +32,13 @@ class MlaArgs(C.Structure):
     ]
 
 
+def _expand_budget_bytes():
+    """Largest bf16 copy of a quantised latent pool the tensor-core route may allocate
+    (FA_B200_MLA_EXPAND_MAX_GB, default 16; 0 keeps quantised latents on the fused kernel)."""
+    import os
+    return int(float(os.environ.get("FA_B200_MLA_EXPAND_MAX_GB", "16")) * (1 << 30))
+
+
 def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, scale_l, scale, causal=False,
                q_offset=0, *, out_dtype=None, return_lse=False, chunk_hint=0, out=None, lse_out=None, engine_hint=0):
     lib = _lib.load()
@@ -82,6 +89,7 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
     else:
         raise RuntimeError("l_pool must be bfloat16, uint8 E4M3 [.., DQK] or uint8 packed NVFP4 [.., DQK/2]")
 
+    q_in = q
     q = q.contiguous().to(q_t)
     l_pool, block_table = l_pool.contiguous(), block_table.contiguous()
     dev = q.device
@@ -105,8 +113,14 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
         q_offset = 0
 
     rows32 = 16 * ((H_q * N_q + 31) // 32)          # the planner counts 16-row tiles; this kernel uses 32
-    tc_shape = (fmt == FA_BF16 and DQK == 576 and DV == 512 and page_size % 64 == 0
-                and page_size & (page_size - 1) == 0 and engine_hint != 2)
+    tc_geometry = (DQK == 576 and DV == 512 and page_size % 64 == 0 and page_size & (page_size - 1) == 0
+                   and engine_hint != 2)
+    # Quantised latents reach the tensor-core kernels through a bf16 copy of the tokens in use (one
+    # elementwise pass, fa_mla_expand_latent): worth it when the head rows fill an MMA tile and the copy
+    # fits the budget; otherwise the fused mma.sync kernel dequantises tile by tile.
+    expand = (tc_geometry and fmt in (FA_E4M3, FA_NVFP4) and H_q * N_q >= 64
+              and l_pool.shape[0] * page_size * DQK * 2 <= _expand_budget_bytes())
+    tc_shape = tc_geometry and (fmt == FA_BF16 or expand)
     if tc_shape:
         # the tensor-core kernel stages at most 128 block-table entries per CTA: bound the key ranges
         cap = lib.fa_mla_tc_max_range(page_size)
@@ -114,6 +128,18 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
     items, n_items, n_slots, max_range, _ = _decode.plan(lens, n_max, B, 1, rows32, page_size, dev, int(chunk_hint))
     ws, cnt = _decode.workspace(dev, lib.fa_mla_workspace_bytes(n_slots, H_q, N_q, DV),
                                 lib.fa_mla_counters_len(B, H_q, N_q))
+    if expand:
+        lib.fa_mla_expand_latent.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_int,
+                                             C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        wide = torch.empty((l_pool.shape[0], page_size, 1, DQK), dtype=torch.bfloat16, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.fa_mla_expand_latent(l_pool.data_ptr(), fmt, l_micro.data_ptr() if l_micro is not None else None,
+                                                tok_scale.data_ptr() if tok_scale is not None else None, float(l_scale),
+                                                block_table.data_ptr(), n_logical, l_pool.shape[0], page_size, items.data_ptr(),
+                                                n_items, DQK, wide.data_ptr(), torch.cuda.current_stream(dev).cuda_stream),
+                       "fa_mla_expand_latent")
+        l_pool, l_micro, tok_scale, l_scale, fmt, q_t = wide, None, None, 1.0, FA_BF16, torch.bfloat16
+        q = q_in.contiguous().to(torch.bfloat16)
     a = MlaArgs()
     a.q, a.q_dtype = q.data_ptr(), _TORCH_TO_FA[q_t]
     a.l_pool, a.latent_dtype = l_pool.data_ptr(), fmt

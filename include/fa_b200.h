@@ -256,6 +256,17 @@ FA_API size_t fa_mla_counters_len(int B, int H_q, int N_q);
 FA_API size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV);
 FA_API int fa_mla_tc_max_range(int page_size);
 FA_API int fa_mla_decode_fwd(const fa_mla_args* args);
+/* Expand the tokens of the planned key ranges of a quantised latent pool into a bf16 pool of the same
+ * shape [num_blocks, page_size, 1, dqk] (rows of other tokens are not touched), the operand of the
+ * tensor-core MLA kernels:
+ *   FA_E4M3 : out[row, :] = bf16(e4m3(l_pool[row, :]) * token_scale[row])   (token_scale null: tensor_scale)
+ *   FA_NVFP4: out[row, 16 j + i] = bf16(e2m1(code) * e4m3(l_micro[row, j]) * tensor_scale), two codes per byte
+ * `items` are the ranges of fa_decode_plan (device memory).  The dequantisation is the one the reference
+ * oracle applies to the same bytes (fa_kernels/reference.py:84-111: dequantize_nvfp4 / FP8 x scale), rounded
+ * once to bf16. */
+FA_API int fa_mla_expand_latent(const void* l_pool, int latent_dtype, const uint8_t* l_micro, const float* token_scale,
+                                float tensor_scale, const int32_t* block_table, int n_logical, int num_blocks, int page_size,
+                                const fa_decode_item* items, int n_items, int dqk, void* out_bf16, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * KV-cache formats and the paged layout (bit-exact with the reference's torch functions).
