@@ -23,7 +23,7 @@
 // first): scores run up to two tiles ahead of the oldest unfinished P V, so softmax overlaps the MMAs.
 //
 // Warps: 0 = TMA producer (own keys), 1 = TMEM owner (+ MMA issuer in the even CTA), 2..5 = softmax /
-// epilogue, 6 = TMA producer (peer keys).
+// epilogue, 6 = TMA producer (peer keys), 7 = second MMA issuer (P V) in the even CTA.
 // Every wait is bounded (sm100.cuh); the only unbounded synchronisation is the cluster barrier, which
 // both CTAs always reach.
 //
@@ -40,7 +40,7 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kPThreads = 224;
+constexpr int kPThreads = 256;
 constexpr int kPDQK = 576, kPDV = 512;
 constexpr int kPBlk = 64 * 128;               // bytes of one [64 rows][64 bf16] block
 constexpr int kPQT = 256;                     // query dims held in tensor memory
@@ -126,16 +126,6 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[3
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
-}
-// non-blocking poll (try_wait may park the thread for a while when the phase is still open)
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
 }
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
@@ -296,89 +286,68 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0 && n_tiles > 0) {
-      // ------------------------------------------------- MMA issuer (even CTA, for the pair)
-      // Scores of up to two tiles ahead of the oldest unfinished P V; whichever is ready is issued, P V first.
+      // ------------------------------------------------- score MMA issuer (even CTA, for the pair)
+      // Two issuing threads (this one and warp 7) keep the tensor pipe fed across batch boundaries: while
+      // one is blocked behind its own batch the other has the next one queued.  Scores run at most two
+      // tiles ahead of the P V: tile j reuses the score buffer of tile j - 2, free once P of j - 2 is out.
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, true, false, false);
-      constexpr uint32_t idesc_pv = idesc_f16(128, 256, true, false, true);
       bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, P2_ERR_Q) && mbar_wait(bar(QT_READY), 0, s_abort, p.status, P2_ERR_QT);
-      int next_qk = 0, next_pv = 0;
-      bool z_sent = false;
-      long long idle_since = 0;
-      while (ok && next_pv < n_tiles) {
-        bool issued = false;
-        // poll the three barriers back to back (each poll is a shared-memory round trip), then decide
-        const bool have_pv = next_pv < next_qk;
-        const bool have_qk = next_qk < n_tiles && next_qk < next_pv + 2;
-        const int pj = next_pv, qj = min(next_qk, n_tiles - 1);
-        const bool r_ok = mbar_test(bar(R_FULL + (pj & 1)), (pj >> 1) & 1);
-        const bool p_ok = mbar_test(bar(P_READY + (pj & 1)), (pj >> 1) & 1);
-        const bool x_ok = mbar_test(bar(X_FULL + (qj & 1)), (qj >> 1) & 1);
-        if (have_pv) {
-          const int j = next_pv, bf = j & 1;
-          const bool last = (j + 1 == n_tiles);
-          if (r_ok && last && ragged_end && !z_sent) {
-            // everything of the last tile has landed in both CTAs: let the softmax threads clear the
-            // value rows past the end of the sequence
-            mbar_arrive(bar(Z_GO));
-            mbar_arrive_cluster(map_to_cta(bar(Z_GO), 1));
-            z_sent = true;
-          }
-          if (r_ok && p_ok) {
-            PAIR_TRACE(1, j, 3);
-            tc_fence_after();
-            const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), p_base = smem_u32(sP + bf * 2 * kPBlk);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int bf = j & 1;
+        if (j >= 2) ok = mbar_wait(bar(P_READY + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_P_READY);
+        if (ok) ok = mbar_wait(bar(X_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
+        if (!ok) break;
+        PAIR_TRACE(1, j, 0);
+        tc_fence_after();
+        const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), d_s = tm_s + 64 * bf;
 #pragma unroll
-            for (int s = 0; s < 2; ++s) {
+        for (int k = 0; k < kPQT / 16; ++k)          // leading query dims from tensor memory
+          mma2_ts(d_s, tm_q + k * 8, smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
+        ok = mbar_wait(bar(X_FULLB + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
-              for (int ks = 0; ks < 8; ++ks) {
-                const int h = ks >> 2;
-                mma2_ss(tm_o + 128 * s, smem_desc_sw128(p_base + h * kPBlk + (ks & 3) * 32, 16, 1024),
-                        smem_desc_sw128(t_base + (4 * s + 2 * h) * kPBlk + (ks & 3) * 2048, kPBlk, 1024), idesc_pv,
-                        (j > 0 || ks > 0) ? 1u : 0u);
-              }
-              mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
-            }
-            PAIR_TRACE(1, j, 4);
-            ++next_pv;
-            issued = true;
-          }
+        for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // the other query dims from shared memory
+          const int kq = k - kPQT / 16;
+          mma2_ss(d_s, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kPBlk + (kq & 3) * 32, 16, 1024),
+                  smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
         }
-        if (!issued && have_qk) {
-          const int j = next_qk, bf = j & 1;
-          if (x_ok) {
-            PAIR_TRACE(1, j, 0);
-            tc_fence_after();
-            const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), d_s = tm_s + 64 * bf;
-#pragma unroll
-            for (int k = 0; k < kPQT / 16; ++k)          // leading query dims from tensor memory
-              mma2_ts(d_s, tm_q + k * 8, smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
-            ok = mbar_wait(bar(X_FULLB + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // the other query dims from shared memory
-              const int kq = k - kPQT / 16;
-              mma2_ss(d_s, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kPBlk + (kq & 3) * 32, 16, 1024),
-                      smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
-            }
-            mma2_commit_both(bar(S_FULL + bf));
-            PAIR_TRACE(1, j, 1);
-            ++next_qk;
-            issued = true;
-          }
+        mma2_commit_both(bar(S_FULL + bf));
+        PAIR_TRACE(1, j, 1);
+      }
+    }
+  } else if (warp == 7) {
+    if (lane == 0 && rank == 0 && n_tiles > 0) {
+      // ------------------------------------------------- P V MMA issuer (even CTA, for the pair)
+      constexpr uint32_t idesc_pv = idesc_f16(128, 256, true, false, true);
+      bool ok = true;
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int bf = j & 1;
+        ok = mbar_wait(bar(R_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_Y_FULL);
+        if (!ok) break;
+        if (ragged_end && j + 1 == n_tiles) {
+          // everything of the last tile has landed in both CTAs: let the softmax threads clear the value
+          // rows past the end of the sequence
+          mbar_arrive(bar(Z_GO));
+          mbar_arrive_cluster(map_to_cta(bar(Z_GO), 1));
         }
-        if (issued) {
-          idle_since = 0;
-        } else {
-          if (*s_abort) break;
-          const long long now = clock64();
-          if (idle_since == 0) idle_since = now;
-          else if (now - idle_since > kWaitCycles) {
-            *s_abort = 1;
-            if (p.status) atomicCAS(p.status, 0, P2_ERR_P_READY);
-            break;
+        ok = mbar_wait(bar(P_READY + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_P_READY);
+        if (!ok) break;
+        PAIR_TRACE(1, j, 3);
+        tc_fence_after();
+        const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), p_base = smem_u32(sP + bf * 2 * kPBlk);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const int h = ks >> 2;
+            mma2_ss(tm_o + 128 * s, smem_desc_sw128(p_base + h * kPBlk + (ks & 3) * 32, 16, 1024),
+                    smem_desc_sw128(t_base + (4 * s + 2 * h) * kPBlk + (ks & 3) * 2048, kPBlk, 1024), idesc_pv,
+                    (j > 0 || ks > 0) ? 1u : 0u);
           }
+          mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
         }
+        PAIR_TRACE(1, j, 4);
       }
     }
   }
