@@ -955,3 +955,28 @@ extern "C" int fa_merge_partials(const float* o_parts, const float* lse_parts, i
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }
+
+extern "C" int fa_paged_decode_host(const fa_decode_host_args* h) {
+  FA_CHECK_ARG(h != nullptr, "fa_paged_decode_host: null args");
+  FA_CHECK_ARG(h->q_host && h->block_table_host && h->out_host && h->items_host, "fa_paged_decode_host: null host buffer");
+  FA_CHECK_ARG(h->dev.q && h->dev.block_table && h->dev.items && h->dev.out, "fa_paged_decode_host: null device staging buffer");
+  FA_CHECK_ARG(h->max_items >= 1, "fa_paged_decode_host: max_items must be >= 1");
+  fa_decode_args a = h->dev;
+  FA_CHECK_ARG(a.B >= 1 && a.H_kv >= 1 && a.H_q >= 1 && a.N_q >= 1 && a.H_q % a.H_kv == 0, "fa_paged_decode_host: bad B/H/N_q");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a.stream);
+  FA_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a.q), h->q_host, h->q_bytes, cudaMemcpyHostToDevice, st));
+  FA_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(a.block_table), h->block_table_host, h->block_table_bytes, cudaMemcpyHostToDevice, st));
+  int n_items = 0, max_range = 0;
+  const int rc = fa_decode_plan(h->seq_lens_host, h->n_k, a.B, a.H_kv, (a.H_q / a.H_kv) * a.N_q, a.page_size, device_sm_count(),
+                                h->chunk_hint, h->items_host, h->max_items, &n_items, &max_range);
+  if (rc != FA_OK) return rc;
+  FA_CUDA_OK(cudaMemcpyAsync(const_cast<fa_decode_item*>(a.items), h->items_host, (size_t)n_items * sizeof(fa_decode_item),
+                             cudaMemcpyHostToDevice, st));
+  a.n_items = n_items;
+  a.n_slots = n_items > a.B ? n_items : 0;
+  a.max_range_keys = max_range;
+  const int rc2 = fa_paged_decode_fwd(&a);
+  if (rc2 != FA_OK) return rc2;
+  FA_CUDA_OK(cudaMemcpyAsync(h->out_host, a.out, h->out_bytes, cudaMemcpyDeviceToHost, st));
+  return FA_OK;
+}

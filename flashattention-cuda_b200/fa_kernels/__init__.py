@@ -32,3 +32,12 @@ def attention(q, k, v, *, causal: bool = False, scale: float | None = None, back
         scale = 1.0 / (q.shape[-1] ** 0.5)
     module = get_backend(backend)
     return module.forward(q, k, v, scale, causal, **kw)
+
+
+def __getattr__(name):
+    # extensions that need torch and the CUDA library are resolved on first use, so that
+    # `import fa_kernels` keeps working without either
+    if name == "HostDecodeStep":
+        from ._decode import HostDecodeStep
+        return HostDecodeStep
+    raise AttributeError(f"module 'fa_kernels' has no attribute {name!r}")

@@ -249,3 +249,106 @@ def merge_partials(o_parts, lse_parts, out_dtype=torch.float32, return_lse=False
                                          out.data_ptr(), _TORCH_TO_FA[out_dtype], lse.data_ptr() if lse is not None else None,
                                          torch.cuda.current_stream(o_parts.device).cuda_stream), "fa_merge_partials")
     return (out, lse) if return_lse else out
+
+
+class DecodeHostArgs(C.Structure):
+    _fields_ = [
+        ("dev", _lib.DecodeArgs),
+        ("q_host", C.c_void_p), ("q_bytes", C.c_size_t),
+        ("block_table_host", C.c_void_p), ("block_table_bytes", C.c_size_t),
+        ("seq_lens_host", C.c_void_p), ("n_k", C.c_int),
+        ("out_host", C.c_void_p), ("out_bytes", C.c_size_t),
+        ("items_host", C.c_void_p), ("max_items", C.c_int), ("chunk_hint", C.c_int),
+    ]
+
+
+class HostDecodeStep:
+    """A paged GQA decode step that starts and ends in HOST memory (C ABI `fa_paged_decode_host`): one call
+    enqueues the copies of q and the block table, the plan for this step's lengths, the decode kernel and
+    the copy of the output back, with no Python or allocator work between the launches.  The fp16 / bf16
+    KV pools stay resident on the device; staging buffers, plan staging, workspace and counters are
+    allocated once per batch shape.  An extension: the reference's `gqa_attention`
+    (fa_kernels/paged.py:379-402) takes CUDA tensors and leaves the copies to the caller.
+
+        step = HostDecodeStep(k_pool, v_pool, page_size, B, H_q, N_q, d, n_logical)
+        step(q_host, block_table_host, seq_lens_host, out_host)     # pinned CPU tensors; enqueues only
+        torch.cuda.current_stream().synchronize()                   # out_host is valid now
+    """
+
+    _RING = 4
+
+    def __init__(self, k_pool, v_pool, page_size, B, H_q, N_q, d, n_logical, *, scale=None, causal=False,
+                 out_dtype=torch.float16):
+        lib = _lib.load()
+        lib.fa_paged_decode_host.argtypes = [C.POINTER(DecodeHostArgs)]
+        _require(k_pool.is_cuda and v_pool.is_cuda and k_pool.dtype == v_pool.dtype
+                 and k_pool.dtype in (torch.float16, torch.bfloat16), "HostDecodeStep takes fp16 or bf16 CUDA pools")
+        _require(k_pool.dim() == 4 and k_pool.shape[1] == page_size and k_pool.shape[3] == d and v_pool.shape == k_pool.shape,
+                 "pools must be [num_blocks, page_size, H_kv, d]")
+        _require(out_dtype in _TORCH_TO_FA, "out_dtype must be float32, float16 or bfloat16")
+        dev = k_pool.device
+        H_kv = k_pool.shape[2]
+        _require(H_q % H_kv == 0, "H_q must be a multiple of H_kv")
+        self.lib, self.dev, self.shape = lib, dev, (B, H_q, N_q, d)
+        self.k_pool, self.v_pool = k_pool.contiguous(), v_pool.contiguous()
+        self.q_t = k_pool.dtype
+        self.out_dtype = out_dtype
+        self.n_logical = int(n_logical)
+        self.q_dev = torch.empty((B, H_q, N_q, d), dtype=self.q_t, device=dev)
+        self.bt_dev = torch.empty((B, n_logical), dtype=torch.int32, device=dev)
+        self.out_dev = torch.empty((B, H_q, N_q, d), dtype=out_dtype, device=dev)
+        self.max_items = int(lib.fa_decode_plan_max_items(None, n_logical * page_size, B, page_size))
+        self.items_dev = torch.empty((self.max_items, 8), dtype=torch.int32, device=dev)
+        self.items_host = [torch.empty((self.max_items, 8), dtype=torch.int32).pin_memory() for _ in range(self._RING)]
+        self.items_done = [None] * self._RING
+        self.turn = 0
+        self.ws = torch.empty(int(lib.fa_decode_workspace_bytes(self.max_items, H_q, N_q, d)), dtype=torch.uint8, device=dev)
+        self.cnt = torch.zeros(int(lib.fa_decode_counters_len(B, H_q, H_kv, N_q)), dtype=torch.int32, device=dev)
+        h = DecodeHostArgs()
+        a = h.dev
+        a.q, a.q_dtype = self.q_dev.data_ptr(), _TORCH_TO_FA[self.q_t]
+        a.k_pool, a.v_pool, a.kv_dtype = self.k_pool.data_ptr(), self.v_pool.data_ptr(), _TORCH_TO_FA[self.q_t]
+        a.k_scale = a.v_scale = 1.0
+        a.block_table, a.n_logical, a.num_blocks, a.page_size = self.bt_dev.data_ptr(), self.n_logical, k_pool.shape[0], int(page_size)
+        a.B, a.H_q, a.H_kv, a.N_q, a.D = B, H_q, H_kv, N_q, d
+        a.softmax_scale = float(scale) if scale is not None else 1.0 / d ** 0.5
+        a.causal, a.q_offset = int(bool(causal)), 0
+        a.items = self.items_dev.data_ptr()
+        a.out, a.out_dtype = self.out_dev.data_ptr(), _TORCH_TO_FA[out_dtype]
+        a.workspace, a.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+        a.counters, a.counters_len = self.cnt.data_ptr(), self.cnt.numel()
+        h.max_items = self.max_items
+        self.h = h
+
+    def __call__(self, q_host, block_table_host, seq_lens_host, out_host, *, q_offset=0, chunk_hint=0):
+        B, H_q, N_q, d = self.shape
+        _require(not q_host.is_cuda and q_host.dtype == self.q_t and q_host.is_contiguous() and tuple(q_host.shape) == self.shape,
+                 "q_host must be a contiguous CPU tensor [B,H_q,N_q,d] in the pools' dtype")
+        _require(block_table_host.dtype == torch.int32 and block_table_host.is_contiguous()
+                 and tuple(block_table_host.shape) == (B, self.n_logical), "block_table_host must be int32 [B, n_logical] on the CPU")
+        _require(out_host.dtype == self.out_dtype and out_host.is_contiguous() and tuple(out_host.shape) == self.shape,
+                 "out_host must be a contiguous CPU tensor [B,H_q,N_q,d] in out_dtype")
+        h = self.h
+        if isinstance(seq_lens_host, torch.Tensor):
+            _require(seq_lens_host.dtype == torch.int32 and seq_lens_host.numel() == B and not seq_lens_host.is_cuda,
+                     "seq_lens_host must be an int32 CPU tensor of B entries")
+            h.seq_lens_host, h.n_k = seq_lens_host.data_ptr(), 0
+        else:
+            h.seq_lens_host, h.n_k = None, int(seq_lens_host)
+        i = self.turn
+        self.turn = (i + 1) % self._RING
+        if self.items_done[i] is not None:
+            self.items_done[i].synchronize()                # the plan staging slot is free once its copy has run
+        stream = torch.cuda.current_stream(self.dev)
+        h.q_host, h.q_bytes = q_host.data_ptr(), q_host.numel() * q_host.element_size()
+        h.block_table_host, h.block_table_bytes = block_table_host.data_ptr(), block_table_host.numel() * 4
+        h.out_host, h.out_bytes = out_host.data_ptr(), out_host.numel() * out_host.element_size()
+        h.items_host = self.items_host[i].data_ptr()
+        h.chunk_hint = int(chunk_hint)
+        h.dev.q_offset = int(q_offset)
+        h.dev.stream = stream.cuda_stream
+        with torch.cuda.device(self.dev):
+            _lib.check(self.lib.fa_paged_decode_host(C.byref(h)), "fa_paged_decode_host")
+        if self.items_done[i] is None:
+            self.items_done[i] = torch.cuda.Event()
+        self.items_done[i].record(stream)

@@ -142,6 +142,34 @@ FA_API size_t fa_decode_workspace_bytes(int n_slots, int H_q, int N_q, int D);
 FA_API size_t fa_decode_counters_len(int B, int H_q, int H_kv, int N_q);
 FA_API int fa_paged_decode_fwd(const fa_decode_args* args);
 
+/* One decode step from HOST buffers: what a serving loop does around fa_paged_decode_fwd, in one call and
+ * without Python or allocator work between the launches.  On `dev.stream` it enqueues
+ *   q_host -> dev.q, block_table_host -> dev.block_table        (cudaMemcpyAsync, host to device)
+ *   fa_decode_plan(seq_lens_host / n_k) into items_host, items_host -> dev.items
+ *   the decode kernel (as fa_paged_decode_fwd; dev.n_items / n_slots / max_range_keys are filled in here)
+ *   dev.out -> out_host                                         (device to host)
+ * and returns without synchronising; the result is in out_host once the stream has drained.  `dev` holds
+ * the resident KV pools and DEVICE staging buffers for q, block table, items (capacity max_items) and out,
+ * plus workspace and counters as for fa_paged_decode_fwd.  Host buffers should be pinned (the copies are
+ * asynchronous only then); items_host must be pinned and must not be reused before its copy has finished.
+ * The reference has no such entry point: its wrappers take CUDA tensors (fa_kernels/paged.py:379-402) and
+ * leave the copies to the caller. */
+typedef struct fa_decode_host_args {
+  fa_decode_args dev;
+  const void* q_host;
+  size_t q_bytes;
+  const int32_t* block_table_host;
+  size_t block_table_bytes;
+  const int32_t* seq_lens_host;   /* int32[B] or NULL (then n_k for every sequence) */
+  int n_k;
+  void* out_host;
+  size_t out_bytes;
+  fa_decode_item* items_host;     /* pinned staging for the plan */
+  int max_items;                  /* capacity of items_host and of dev.items */
+  int chunk_hint;                 /* as fa_decode_plan */
+} fa_decode_host_args;
+FA_API int fa_paged_decode_host(const fa_decode_host_args* args);
+
 /* Same computation as fa_paged_decode_fwd for callers that have no device memory to give and cannot
  * obtain any.  (This entry point has no counterpart in the reference, whose host functions allocate
  * their outputs and workspaces with torch on every call.)  Two kinds of host are meant: an inference

@@ -116,6 +116,34 @@ def test_varlen_pages_lse_and_fp16_out(page_size, d):
     assert (out[4] == 0).all()        # the empty sequence returns zeros
 
 
+def test_host_buffer_step_matches_device_api_and_oracle():
+    """fa_paged_decode_host through HostDecodeStep: q, block table and lengths start in pinned host memory,
+    the output ends there; three steps in a row with different lengths (long enough to be split, ragged,
+    empty) reuse the staging buffers and must equal the device-tensor API bit for bit."""
+    from fa_kernels import HostDecodeStep, gqa_attention
+    H_kv, G, d, page_size = 2, 4, 128, 16
+    all_lens = [[1000, 4097, 63, 0], [16, 17, 9000, 5], [4096, 4096, 4096, 4096]]
+    B = 4
+    ks = [randn((H_kv, 9000, d), 300 + i)[1] for i in range(B)]
+    vs = [randn((H_kv, 9000, d), 400 + i)[1] for i in range(B)]
+    kp, bt, _ = paged_varlen(ks, page_size, 33)
+    vp, _, _ = paged_varlen(vs, page_size, 33)
+    kp_d, vp_d = dev(kp, torch.float16), dev(vp, torch.float16)
+    bt_t = torch.from_numpy(np.ascontiguousarray(bt)).to(torch.int32)
+    step = HostDecodeStep(kp_d, vp_d, page_size, B, G * H_kv, 1, d, bt_t.shape[1], out_dtype=torch.float16)
+    bt_host = bt_t.pin_memory()
+    out_host = torch.empty((B, G * H_kv, 1, d), dtype=torch.float16).pin_memory()
+    for it, lens in enumerate(all_lens):
+        q_t, q = randn((B, G * H_kv, 1, d), 50 + it)
+        q_host = q_t.to(torch.float16).pin_memory()
+        step(q_host, bt_host, torch.tensor(lens, dtype=torch.int32).pin_memory(), out_host)
+        torch.cuda.current_stream().synchronize()
+        same = gqa_attention(q_t.cuda(), kp_d, vp_d, bt_t.cuda(), page_size, lens, out_dtype=torch.float16)
+        assert torch.equal(out_host, same.cpu())
+        ref = O.paged_gqa_attention_ref(q, kp, vp, bt, page_size, lens)
+        assert_close(out_host, ref, what=f"host step {it}")
+
+
 def test_split_count_does_not_change_the_result():
     from fa_kernels import gqa_attention
     B, H_kv, G, N_k, d, page_size = 2, 2, 4, 8190, 128, 16
