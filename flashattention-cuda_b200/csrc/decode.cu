@@ -576,43 +576,78 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
   if (s_ticket != it.n_split - 1) return;
   __threadfence();
   if (tid == 0) p.counters[cidx] = 0;   // self-reset for the next launch
-  // One thread per (row, four output columns); the partials of kU ranges are fetched before any is
-  // used, so a merge over n ranges costs about n / kU L2 round trips, with a running maximum.
+  // A thread owns (row, four output columns) and, when there are fewer such columns than threads, one of
+  // `groups` interleaved subsets of the ranges; the partials of kU ranges are fetched before any is used,
+  // so a merge over n ranges costs about n / (kU * groups) L2 round trips, with a running maximum.  The
+  // groups meet in shared memory (the K/V pipeline is drained by now).
   constexpr int D4 = D / 4;
   constexpr int kU = 8;
   const int64_t slot_stride = (int64_t)p.H_q * p.N_q;
-  for (int idx = tid; idx < rows_valid * D4; idx += kThreads) {
-    const int row = idx / D4, d4 = idx - row * D4;
+  const int n_cols = rows_valid * D4;
+  int groups = 1;
+  while (groups * 2 * n_cols <= kThreads && groups * 2 <= it.n_split) groups *= 2;
+  float* s_part = reinterpret_cast<float*>(smem);          // [groups][n_cols][6]: m, l, acc.xyzw
+  static_assert(PIPE_BYTES >= kThreads * 6 * 4, "merge scratch does not fit the pipeline buffers");
+  const int n_work = groups > 1 ? groups * n_cols : n_cols;
+  for (int idx0 = 0; idx0 < n_work; idx0 += kThreads) {
+    const int idx = idx0 + tid;
+    const bool active = idx < n_work;
+    const int grp = groups > 1 ? idx / n_cols : 0;
+    const int col = groups > 1 ? idx - grp * n_cols : idx;
+    const int row = active ? col / D4 : 0, d4 = col - row * D4;
     const int m = m0 + row;
     const int iq = m / p.G, g = m - iq * p.G;
     const int64_t hrow = (int64_t)(h_kv * p.G + g) * p.N_q + iq;
-    const float* lse_base = p.part_lse + it.slot_base * slot_stride + hrow;
-    const float4* o_base = reinterpret_cast<const float4*>(p.part_o + (it.slot_base * slot_stride + hrow) * D) + d4;
     float m_run = -INFINITY, l = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < it.n_split; s0 += kU) {
-      float ls[kU];
-      float4 ov[kU];
+    if (active) {
+      const float* lse_base = p.part_lse + it.slot_base * slot_stride + hrow;
+      const float4* o_base = reinterpret_cast<const float4*>(p.part_o + (it.slot_base * slot_stride + hrow) * D) + d4;
+      const int n_mine = (it.n_split - grp + groups - 1) / groups;       // ranges grp, grp + groups, ...
+      for (int s0 = 0; s0 < n_mine; s0 += kU) {
+        float ls[kU];
+        float4 ov[kU];
 #pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const int sidx = min(s0 + u, it.n_split - 1);
-        ls[u] = __ldcg(lse_base + sidx * slot_stride);
-        ov[u] = __ldcg(o_base + sidx * slot_stride * D4);
-        if (s0 + u >= it.n_split) ls[u] = -INFINITY;
+        for (int u = 0; u < kU; ++u) {
+          const int sidx = grp + groups * min(s0 + u, n_mine - 1);
+          ls[u] = __ldcg(lse_base + sidx * slot_stride);
+          ov[u] = __ldcg(o_base + sidx * slot_stride * D4);
+          if (s0 + u >= n_mine) ls[u] = -INFINITY;
+        }
+        float mb = m_run;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) mb = fmaxf(mb, ls[u]);
+        if (mb == -INFINITY) continue;
+        const float resc = __expf(m_run - mb);
+        acc.x *= resc, acc.y *= resc, acc.z *= resc, acc.w *= resc, l *= resc;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const float wgt = __expf(ls[u] - mb);
+          acc.x += wgt * ov[u].x, acc.y += wgt * ov[u].y, acc.z += wgt * ov[u].z, acc.w += wgt * ov[u].w;
+          l += wgt;
+        }
+        m_run = mb;
       }
-      float mb = m_run;
-#pragma unroll
-      for (int u = 0; u < kU; ++u) mb = fmaxf(mb, ls[u]);
-      if (mb == -INFINITY) continue;
-      const float resc = __expf(m_run - mb);
-      acc.x *= resc, acc.y *= resc, acc.z *= resc, acc.w *= resc, l *= resc;
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const float wgt = __expf(ls[u] - mb);
-        acc.x += wgt * ov[u].x, acc.y += wgt * ov[u].y, acc.z += wgt * ov[u].z, acc.w += wgt * ov[u].w;
-        l += wgt;
+    }
+    if (groups > 1) {            // n_work <= kThreads: a single pass, every thread reaches the barriers
+      float* mine = s_part + (size_t)idx * 6;
+      if (active) {
+        mine[0] = m_run, mine[1] = l, mine[2] = acc.x, mine[3] = acc.y, mine[4] = acc.z, mine[5] = acc.w;
       }
-      m_run = mb;
+      __syncthreads();
+      if (!active || grp != 0) continue;
+      for (int g2 = 1; g2 < groups; ++g2) {
+        const float* o = s_part + ((size_t)g2 * n_cols + col) * 6;
+        const float mb = fmaxf(m_run, o[0]);
+        if (mb == -INFINITY) continue;
+        const float ra = __expf(m_run - mb), rb = __expf(o[0] - mb);
+        acc.x = acc.x * ra + o[2] * rb, acc.y = acc.y * ra + o[3] * rb;
+        acc.z = acc.z * ra + o[4] * rb, acc.w = acc.w * ra + o[5] * rb;
+        l = l * ra + o[1] * rb;
+        m_run = mb;
+      }
+    } else if (!active) {
+      continue;
     }
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
     const int64_t orow = (int64_t)b * p.H_q * p.N_q + hrow;
