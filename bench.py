@@ -99,7 +99,9 @@ class ClockSampler:
 def build_workload(name, device, rank):
     from fa_bench import workloads
     if name == "paged_gqa_decode_fp16":
-        w = workloads.paged_gqa_decode(device, seed=2 + 1000 * rank)
+        # weak scaling: every GPU gets the same amount of work (the seed-2 context lengths and page
+        # permutation of the single-GPU configuration) over its own K, V and q values
+        w = workloads.paged_gqa_decode(device, seed=2, data_seed=2 + 1000 * rank)
         w["describe"] = {"workload": "paged_gqa_decode_fp16", "batch_per_gpu": 64, "h_q": 32, "h_kv": 8, "d": 128,
                          "page_size": 16, "ctx": "uniform[1024,8192] seed 2", "kv_tokens_per_gpu": w["tokens"]}
         return w

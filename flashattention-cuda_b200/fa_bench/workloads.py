@@ -9,9 +9,10 @@ import torch
 
 
 def paged_gqa_decode(device, *, batch=64, h_q=32, h_kv=8, d=128, page_size=16, min_len=1024, max_len=8192,
-                     seed=2, kv_dtype=torch.float16, seq_lens=None):
+                     seed=2, kv_dtype=torch.float16, seq_lens=None, data_seed=None):
     """Paged GQA decode: one query token per sequence, context lengths uniform in [min_len, max_len],
-    block table = random permutation of the physical pages, K/V ~ N(0,1).
+    block table = random permutation of the physical pages, K/V ~ N(0,1).  `seed` draws the lengths and
+    the page permutation, `data_seed` (default: `seed`) the tensor values.
 
     Returns a dict with q, k_pool, v_pool, block_table, page_size, seq_lens (python list) and the
     algorithmic byte counts.
@@ -29,7 +30,7 @@ def paged_gqa_decode(device, *, batch=64, h_q=32, h_kv=8, d=128, page_size=16, m
     for b, np_ in enumerate(n_pages):
         bt[b, :np_] = perm[cur:cur + np_].to(torch.int32)
         cur += np_
-    gd = torch.Generator(device=device).manual_seed(seed)
+    gd = torch.Generator(device=device).manual_seed(seed if data_seed is None else data_seed)
     k_pool = torch.randn(total_pages, page_size, h_kv, d, device=device, dtype=torch.float32, generator=gd).to(kv_dtype)
     v_pool = torch.randn(total_pages, page_size, h_kv, d, device=device, dtype=torch.float32, generator=gd).to(kv_dtype)
     q = torch.randn(batch, h_q, 1, d, device=device, dtype=torch.float32, generator=gd).to(kv_dtype)
