@@ -479,7 +479,8 @@ int launch_mla(const MlaParams& p, int n_items, int row_tiles, cudaStream_t st) 
 
 namespace fa {
 // tensor-core path (mla_tc.cu)
-bool mla_tc_applicable(const fa_mla_args* a);
+bool mla_tc_applicable(const fa_mla_args* a, int max_pages);
+int mla_pair_max_pages();
 size_t mla_tc_workspace_bytes(int n_slots, int M);
 size_t mla_tc_counters_len(int B, int M);
 int launch_mla_tc(const fa_mla_args* a, cudaStream_t st);
@@ -500,6 +501,10 @@ extern "C" size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV) 
 
 // Largest key range (in keys, a multiple of 64) one CTA of the tensor-core kernel can take at this page size.
 extern "C" int fa_mla_tc_max_range(int page_size) { return (126 * page_size) / 64 * 64; }
+extern "C" int fa_mla_pair_max_range(int page_size) {
+  const long long keys = (long long)(mla_pair_max_pages() - 2) * page_size / 128 * 128;
+  return (int)std::min<long long>(keys, 1 << 30);
+}
 
 extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   FA_CHECK_ARG(a != nullptr, "fa_mla_decode_fwd: null args");
@@ -537,12 +542,13 @@ extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
 
   // bf16 (576, 512) latents on 64-token-aligned pages run on tcgen05 unless FA_B200_MLA_TC=0
   static const bool tc_enabled = [] { const char* e = getenv("FA_B200_MLA_TC"); return !(e && e[0] == '0'); }();
-  if (tc_enabled && a->engine_hint != 2 && mla_tc_applicable(a)) {
+  // the CTA-pair kernel (cta_group::2) unless FA_B200_MLA_PAIR=0 or engine_hint 3 asks for the single-CTA one
+  static const bool pair_enabled = [] { const char* e = getenv("FA_B200_MLA_PAIR"); return !(e && e[0] == '0'); }();
+  const bool want_pair = pair_enabled && a->engine_hint != 3;
+  if (tc_enabled && a->engine_hint != 2 && mla_tc_applicable(a, want_pair ? mla_pair_max_pages() : 0)) {
     if (a->workspace_bytes < mla_tc_workspace_bytes(a->n_slots, M))
       return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, mla_tc_workspace_bytes(a->n_slots, M));
-    // the CTA-pair kernel (cta_group::2) unless FA_B200_MLA_PAIR=0 asks for the single-CTA one
-    static const bool pair_enabled = [] { const char* e = getenv("FA_B200_MLA_PAIR"); return !(e && e[0] == '0'); }();
-    if (pair_enabled && a->engine_hint != 3)
+    if (want_pair)
       return launch_mla_pair(a, mla_tc_counters_len(a->B, M) - 1, reinterpret_cast<cudaStream_t>(a->stream));
     return launch_mla_tc(a, reinterpret_cast<cudaStream_t>(a->stream));
   }

@@ -45,7 +45,7 @@ constexpr int kPDQK = 576, kPDV = 512;
 constexpr int kPBlk = 64 * 128;               // bytes of one [64 rows][64 bf16] block
 constexpr int kPQT = 256;                     // query dims held in tensor memory
 constexpr int kPQB = (kPDQK - kPQT) / 64;     // query blocks in shared memory
-constexpr int kPMaxPages = 128;
+constexpr int kPMaxPages = 512;          // block-table entries staged per CTA
 constexpr float kPThreshold = 8.f;
 
 struct MlaPairParams {
@@ -593,6 +593,8 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 }  // namespace
 
 // Host side; called by fa_mla_decode_fwd (mla.cu) after validation when the tensor-core path applies.
+int mla_pair_max_pages() { return kPMaxPages; }
+
 int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStream_t st) {
   const int M = a->H_q * a->N_q;
   const int row_tiles = (M + 127) / 128;

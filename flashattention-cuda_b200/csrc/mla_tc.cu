@@ -426,10 +426,12 @@ mla_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 }  // namespace
 
 // Host side; called by fa_mla_decode_fwd (mla.cu) after validation when the tensor-core path applies.
-bool mla_tc_applicable(const fa_mla_args* a) {
+// `max_pages`: block-table entries the chosen kernel stages per CTA (0 = this file's kernel)
+bool mla_tc_applicable(const fa_mla_args* a, int max_pages) {
+  if (max_pages <= 0) max_pages = kTcMaxPages;
   if (a->latent_dtype != FA_BF16 || a->DQK != kTcDQK || a->DV != kTcDV) return false;
   if (a->page_size % 64 != 0 || (a->page_size & (a->page_size - 1)) != 0) return false;
-  if (a->max_range_keys / a->page_size + 2 > kTcMaxPages) return false;
+  if (a->max_range_keys / a->page_size + 2 > max_pages) return false;
   if ((int64_t)a->B * a->H_q * a->N_q > INT_MAX || (int64_t)a->num_blocks * a->page_size > INT_MAX) return false;
   return true;
 }

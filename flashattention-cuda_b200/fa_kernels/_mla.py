@@ -123,8 +123,23 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
     tc_shape = tc_geometry and (fmt == FA_BF16 or expand)
     if tc_shape:
         # the tensor-core kernel stages at most 128 block-table entries per CTA: bound the key ranges
-        cap = lib.fa_mla_tc_max_range(page_size)
-        chunk_hint = min(int(chunk_hint), cap) if chunk_hint else (cap if n_max > cap else 0)
+        import os
+        single = engine_hint == 3 or os.environ.get("FA_B200_MLA_PAIR", "1")[:1] == "0"
+        cap = lib.fa_mla_tc_max_range(page_size) if single else lib.fa_mla_pair_max_range(page_size)
+        if chunk_hint:
+            chunk_hint = min(int(chunk_hint), cap)
+        else:
+            # A key range costs ~15 us of pipeline fill and drain in these kernels (measured), so sequences
+            # stay whole while there is one (sequence, 128-row tile) unit per CTA pair / CTA; fewer units
+            # are cut into about two ranges per slot, never shorter than 2048 keys.
+            slots = max(1, _decode.sm_count(dev) // (1 if single else 2))
+            units = B * ((H_q * N_q + 127) // 128)
+            total = sum(lens) if lens is not None else n_max * B
+            if units >= slots:
+                chunk_hint = cap
+            else:
+                want = -(-total * ((H_q * N_q + 127) // 128) // (2 * slots))
+                chunk_hint = min(cap, max(2048, -(-want // 128) * 128))
     items, n_items, n_slots, max_range, _ = _decode.plan(lens, n_max, B, 1, rows32, page_size, dev, int(chunk_hint))
     ws, cnt = _decode.workspace(dev, lib.fa_mla_workspace_bytes(n_slots, H_q, N_q, DV),
                                 lib.fa_mla_counters_len(B, H_q, N_q))

@@ -282,7 +282,8 @@ typedef struct fa_mla_args {
 } fa_mla_args;
 FA_API size_t fa_mla_counters_len(int B, int H_q, int N_q);
 FA_API size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV);
-FA_API int fa_mla_tc_max_range(int page_size);
+FA_API int fa_mla_tc_max_range(int page_size);     /* longest key range of the single-CTA tcgen05 kernel */
+FA_API int fa_mla_pair_max_range(int page_size);   /* longest key range of the CTA-pair kernel */
 FA_API int fa_mla_decode_fwd(const fa_mla_args* args);
 /* Expand the tokens of the planned key ranges of a quantised latent pool into a bf16 pool of the same
  * shape [num_blocks, page_size, 1, dqk] (rows of other tokens are not touched), the operand of the
