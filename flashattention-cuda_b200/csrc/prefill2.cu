@@ -25,6 +25,14 @@
 namespace fa {
 namespace {
 
+#ifdef FA_P2_TRACE
+__device__ long long g_p2_trace[2][64][8];
+#define P2_TRACE(wgi, j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x % 128 == 0 && (j) < 64) g_p2_trace[wgi][j][slot] = clock64(); } while (0)
+#else
+#define P2_TRACE(wgi, j, slot) do { } while (0)
+#endif
+
+
 using namespace sm100;
 
 constexpr int kP2Threads = 384;
@@ -242,13 +250,16 @@ prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float m_ref = -INFINITY, l_run = 0.f;              // m_ref: the maximum P and O are currently scaled by
     bool ok = true;
     for (int j = 0; j < nt; ++j) {
+      P2_TRACE(i, j, 0);
       ok = mbar_wait(bar(S_FULL + i), j & 1, s_abort, p.status, P2_ERR_S_FULL);
       if (!ok) break;
+      P2_TRACE(i, j, 1);
       tc_fence_after();
       float s[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
       tmem_wait_ld();
+      P2_TRACE(i, j, 2);
 
       const int k0 = j * 128;
       const bool need_mask = (k0 + 128 > p.N_k) || (p.causal && k0 + 127 > q0 + i * 128);
@@ -279,6 +290,7 @@ prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         m_ref = mx;
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      P2_TRACE(i, j, 3);
       const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_use, -m_use);
       uint64_t sums[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
@@ -299,6 +311,7 @@ prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), sum_lo, sum_hi);
       const float sum = sum_lo + sum_hi;
       l_run = l_run * alpha + sum;
+      P2_TRACE(i, j, 4);
       // S_FULL of key tile j implies P V of key tile j-1 has finished (same issuing thread, in order),
       // so O may be rescaled here
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
@@ -324,6 +337,7 @@ prefill2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(P_READY + i));
+      P2_TRACE(i, j, 5);
     }
     if (ok && nt > 0) ok = mbar_wait(bar(O_DONE + i), 0, s_abort, p.status, P2_ERR_O_DONE);
     if (ok && nt > 0) {
@@ -434,5 +448,11 @@ int launch_prefill2(const fa_dense_args* a, float scale_log2, cudaStream_t st) {
   FA_P2(64, false)
 #undef FA_P2
 }
+
+#ifdef FA_P2_TRACE
+extern "C" __attribute__((visibility("default"))) int fa_debug_p2_trace(long long* dst, int n) {
+  return (int)cudaMemcpyFromSymbol(dst, g_p2_trace, sizeof(long long) * (size_t)n);
+}
+#endif
 
 }  // namespace fa
