@@ -396,7 +396,7 @@ def run_long_decode(args):
 
 # DRAM bytes per launch of the decode kernel from the committed ncu capture
 # (profiles/paged_decode_fp16_config3.md), or None until one exists.
-TRAFFIC_BYTES_PER_LAUNCH = 1312048592   # 1.303458 GB read + 8.59 MB written
+TRAFFIC_BYTES_PER_LAUNCH = 1303611000   # 1.299411 GB read + 4.20 MB written (mean of two captured launches)
 
 
 def _use_all_host_threads():
