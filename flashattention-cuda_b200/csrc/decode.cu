@@ -1002,7 +1002,10 @@ extern "C" int fa_paged_decode_host(const fa_decode_host_args* h) {
   FA_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a.q), h->q_host, h->q_bytes, cudaMemcpyHostToDevice, st));
   FA_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(a.block_table), h->block_table_host, h->block_table_bytes, cudaMemcpyHostToDevice, st));
   int n_items = 0, max_range = 0;
-  const int rc = fa_decode_plan(h->seq_lens_host, h->n_k, a.B, a.H_kv, (a.H_q / a.H_kv) * a.N_q, a.page_size, device_sm_count(),
+  // as the Python host does: the fp16 / bf16 kernel at d = 128 runs two CTAs per SM, the planner counts three
+  const int sms = device_sm_count();
+  const int plan_sms = ((a.kv_dtype == FA_F16 || a.kv_dtype == FA_BF16) && a.D == 128) ? (2 * sms + 2) / 3 : sms;
+  const int rc = fa_decode_plan(h->seq_lens_host, h->n_k, a.B, a.H_kv, (a.H_q / a.H_kv) * a.N_q, a.page_size, plan_sms,
                                 h->chunk_hint, h->items_host, h->max_items, &n_items, &max_range);
   if (rc != FA_OK) return rc;
   FA_CUDA_OK(cudaMemcpyAsync(const_cast<fa_decode_item*>(a.items), h->items_host, (size_t)n_items * sizeof(fa_decode_item),

@@ -37,11 +37,13 @@ def sm_count(device) -> int:
     return _sm_count[key]
 
 
-def plan(seq_lens, n_k: int, B: int, H_kv: int, rows: int, page_size: int, device, chunk_hint: int = 0):
+def plan(seq_lens, n_k: int, B: int, H_kv: int, rows: int, page_size: int, device, chunk_hint: int = 0,
+         ctas_per_sm: int = 3):
     """Return (items_device_tensor, n_items, n_slots, max_range_keys); cached per argument set.
 
-    `seq_lens` is None (every sequence has n_k keys) or a tuple of B ints."""
-    key = (seq_lens, n_k, B, H_kv, rows, page_size, str(device), chunk_hint)
+    `seq_lens` is None (every sequence has n_k keys) or a tuple of B ints.  The planner counts three CTA
+    slots per SM; a kernel that fits fewer (`ctas_per_sm`) is planned for proportionally fewer SMs."""
+    key = (seq_lens, n_k, B, H_kv, rows, page_size, str(device), chunk_hint, ctas_per_sm)
     hit = _plan_cache.get(key)
     if hit is not None:
         return hit
@@ -54,7 +56,8 @@ def plan(seq_lens, n_k: int, B: int, H_kv: int, rows: int, page_size: int, devic
     cap = lib.fa_decode_plan_max_items(lens_ptr, int(n_k), B, page_size)
     host, done = _staging(device, cap)
     n_items, max_range = C.c_int(0), C.c_int(0)
-    _lib.check(lib.fa_decode_plan(lens_ptr, int(n_k), B, H_kv, rows, page_size, sm_count(device), chunk_hint,
+    sms = -(-sm_count(device) * int(ctas_per_sm) // 3)
+    _lib.check(lib.fa_decode_plan(lens_ptr, int(n_k), B, H_kv, rows, page_size, sms, chunk_hint,
                                   host.data_ptr(), cap, C.byref(n_items), C.byref(max_range)), "fa_decode_plan")
     n = n_items.value
     items = torch.empty((n, 8), dtype=torch.int32, device=device)
@@ -195,7 +198,9 @@ def paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal=F
         _require(q_offsets_t.numel() == B, "per-sequence q_offset must have B entries")
         q_offset = 0
     G = H_q // H_kv
-    items, n_items, n_slots, max_range, _ = plan(lens, n_max, B, H_kv, G * N_q, page_size, dev, int(chunk_hint))
+    # the fp16 / bf16 kernel at d = 128 keeps three 32 KB stages per CTA: two CTAs per SM, the others three
+    ctas = 2 if (kv_format in ("f16", "bf16") and d == 128) else 3
+    items, n_items, n_slots, max_range, _ = plan(lens, n_max, B, H_kv, G * N_q, page_size, dev, int(chunk_hint), ctas)
     ws, cnt = workspace(dev, lib.fa_decode_workspace_bytes(n_slots, H_q, N_q, d),
                         lib.fa_decode_counters_len(B, H_q, H_kv, N_q))
 
