@@ -725,7 +725,7 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
                               int* n_items, int* max_range_keys) {
   FA_CHECK_ARG(B >= 1 && H_kv >= 1 && rows >= 1 && page_size >= 1, "fa_decode_plan: B, H_kv, rows, page_size must be >= 1");
   FA_CHECK_ARG(items && n_items && max_range_keys, "fa_decode_plan: null output pointer");
-  if (num_sms <= 0) num_sms = 148;
+  if (num_sms == 0) num_sms = 148;
   const int row_tiles = (rows + kRowTile - 1) / kRowTile;
   int64_t total = 0;
   for (int b = 0; b < B; ++b) {
@@ -733,28 +733,23 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     FA_CHECK_ARG(len >= 0, "fa_decode_plan: negative sequence length at b=%d", b);
     total += len;
   }
-  // Every range pays a fixed start-up (metadata, block table, pipeline fill; worth ~300 keys), so
-  // sequences are cut only when there are fewer (sequence, head, row tile) units than CTA slots (up to
-  // 3 per SM).  Equal ranges would end with a partly filled last wave as long as one range, so the
-  // ranges shrink instead (guided scheduling): with `share` = keys per slot under perfect balance, each
-  // sequence gives half of what is left of it to ranges of `share` keys, half of the rest to ranges of
-  // share/2, ... down to a floor of 1024 keys; launched longest first, the short ranges fill the tail.
-  // Every level then holds about slots/2 ranges, so no level spills into a second wave of its own.
-  // (Measured on B200, FP8 KV, B=4, 8 KV heads: 1 Mi-key contexts 1810 -> 1691 us against eight equal
-  // waves, 256 Ki-key contexts 553 -> 453 us.)
+  // Every range pays a fixed start-up (metadata, block table, pipeline fill; worth 300-500 keys), and a
+  // launch ends with its last wave.  Candidates: whole sequences (longest first); two or three equal
+  // ranges per sequence; shrinking ranges (guided scheduling): with `share` = keys per slot under perfect
+  // balance, each sequence gives half of what is left of it to ranges of `share` keys, half of the rest to
+  // ranges of share/2, ... down to a floor of 1024 keys, so that the short ranges fill the tail and every
+  // level holds about slots/2 ranges.  The candidate with the shortest list-scheduling estimate is taken;
+  // with many waves of whole sequences (>= 6 per slot) nothing is cut.
+  // (Measured on B200: FP8 KV, B=4, 8 KV heads, 1 Mi-key contexts 1810 -> 1691 us against eight equal
+  // waves; fp16, 8 KV heads, 8192-key contexts: 55 sequences 330 -> 294 us, 80 sequences 477 -> 457 us.)
   const int64_t max_chunk = (int64_t)(kMaxPages - 1) * page_size / kTN * kTN;
   FA_CHECK_ARG(max_chunk >= kTN, "fa_decode_plan: page_size too small");
-  const int64_t slots = (int64_t)num_sms * 3;
+  const int64_t slots = num_sms > 0 ? (int64_t)num_sms * 3 : -(int64_t)num_sms;   // negative: the slot count itself
   const int64_t units = (int64_t)B * H_kv * row_tiles;
   const int64_t work = total * H_kv * row_tiles;      // keys x heads x row tiles
   auto round_tile = [](int64_t x) { return std::max<int64_t>((x + kTN - 1) / kTN * kTN, kTN); };
-  bool guided = false;
   int64_t chunk = max_chunk;
-  if (chunk_hint > 0) {
-    chunk = chunk_hint;
-  } else if (units < slots) {
-    guided = true;
-  }
+  if (chunk_hint > 0) chunk = chunk_hint;
   chunk = std::min(round_tile(chunk), max_chunk);
 
   static const double first_frac = env_double("FA_B200_PLAN_FIRST", 1.0);
@@ -764,15 +759,18 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
   // small jobs: let the floor fall to 256 keys so that there are still ranges for every slot
   const int64_t floor_chunk = std::min(std::min(round_tile(floor_keys), std::max<int64_t>(round_tile(share / 2), 256)), max_chunk);
 
-  std::vector<fa_decode_item> v;
+  // one candidate plan: whole sequences (cut only at `chunk`) or shrinking ranges
+  auto build = [&](bool guided, int parts, std::vector<fa_decode_item>& v, int& max_range) {
   std::vector<int64_t> cuts;
   int slot = 0;
-  int max_range = 0;
+  max_range = 0;
+  v.clear();
   for (int b = 0; b < B; ++b) {
     const int len = seq_lens_host ? seq_lens_host[b] : n_k;
     cuts.clear();                                       // range boundaries after 0
     if (!guided) {
       int ns = (int)std::max<int64_t>((len + chunk - 1) / chunk, 1);
+      if (parts > 1 && len >= (int64_t)parts * 512) ns = std::max(ns, parts);   // `parts` equal ranges per sequence
       const int64_t cb = round_tile((len + ns - 1) / ns);
       ns = (int)std::max<int64_t>((len + cb - 1) / cb, 1);
       for (int s2 = 1; s2 <= ns; ++s2) cuts.push_back(std::min<int64_t>((int64_t)s2 * cb, len));
@@ -808,6 +806,49 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
       v.push_back(it);
     }
     slot += ns;
+  }
+  };
+  // Estimated length of the launch: every (range, head, row tile) CTA costs its keys plus the start-up,
+  // CTAs take the slots in launch order (longest range first), all at the same rate.
+  auto estimate = [&](std::vector<fa_decode_item>& v) {
+    std::stable_sort(v.begin(), v.end(), [](const fa_decode_item& a, const fa_decode_item& b2) {
+      return (a.k_end - a.k_begin) > (b2.k_end - b2.k_begin);
+    });
+    std::vector<int64_t> heap((size_t)slots, 0);
+    auto later = [](int64_t x, int64_t y) { return x > y; };
+    int64_t makespan = 0;
+    const int per_item = H_kv * row_tiles;
+    for (const fa_decode_item& it : v)
+      for (int u = 0; u < per_item; ++u) {
+        std::pop_heap(heap.begin(), heap.end(), later);
+        heap.back() += (it.k_end - it.k_begin) + 500;
+        makespan = std::max(makespan, heap.back());
+        std::push_heap(heap.begin(), heap.end(), later);
+      }
+    return makespan;
+  };
+  std::vector<fa_decode_item> v;
+  int max_range = 0;
+  if (chunk_hint > 0 || units >= 6 * slots) {
+    build(false, 1, v, max_range);                       // as asked, or enough whole sequences for many waves
+  } else {
+    // few waves: whole sequences leave the last wave partly empty; two or three equal ranges per sequence,
+    // or shrinking ranges, fill it at the price of a start-up (~500 keys) per range.  Take the candidate
+    // with the shortest estimated launch.
+    build(false, 1, v, max_range);
+    int64_t best = estimate(v);
+    std::vector<fa_decode_item> alt;
+    int alt_range = 0;
+    for (int cand = 0; cand < 3; ++cand) {
+      if (cand == 0) build(true, 1, alt, alt_range);
+      else build(false, cand + 1, alt, alt_range);
+      const int64_t t = estimate(alt);
+      if (t < best) {
+        best = t;
+        v = alt;
+        max_range = alt_range;
+      }
+    }
   }
   std::stable_sort(v.begin(), v.end(), [](const fa_decode_item& a, const fa_decode_item& b2) {
     return (a.k_end - a.k_begin) > (b2.k_end - b2.k_begin);
@@ -1004,7 +1045,7 @@ extern "C" int fa_paged_decode_host(const fa_decode_host_args* h) {
   int n_items = 0, max_range = 0;
   // as the Python host does: the fp16 / bf16 kernel at d = 128 runs two CTAs per SM, the planner counts three
   const int sms = device_sm_count();
-  const int plan_sms = ((a.kv_dtype == FA_F16 || a.kv_dtype == FA_BF16) && a.D == 128) ? (2 * sms + 2) / 3 : sms;
+  const int plan_sms = ((a.kv_dtype == FA_F16 || a.kv_dtype == FA_BF16) && a.D == 128) ? -2 * sms : sms;
   const int rc = fa_decode_plan(h->seq_lens_host, h->n_k, a.B, a.H_kv, (a.H_q / a.H_kv) * a.N_q, a.page_size, plan_sms,
                                 h->chunk_hint, h->items_host, h->max_items, &n_items, &max_range);
   if (rc != FA_OK) return rc;

@@ -56,7 +56,7 @@ def plan(seq_lens, n_k: int, B: int, H_kv: int, rows: int, page_size: int, devic
     cap = lib.fa_decode_plan_max_items(lens_ptr, int(n_k), B, page_size)
     host, done = _staging(device, cap)
     n_items, max_range = C.c_int(0), C.c_int(0)
-    sms = -(-sm_count(device) * int(ctas_per_sm) // 3)
+    sms = sm_count(device) if int(ctas_per_sm) == 3 else -sm_count(device) * int(ctas_per_sm)
     _lib.check(lib.fa_decode_plan(lens_ptr, int(n_k), B, H_kv, rows, page_size, sms, chunk_hint,
                                   host.data_ptr(), cap, C.byref(n_items), C.byref(max_range)), "fa_decode_plan")
     n = n_items.value

@@ -77,7 +77,10 @@ typedef struct fa_decode_item {
  * similar-sized ranges, longest first.
  *   seq_lens_host : host int32[B] per-sequence key counts, or NULL to use n_k for every sequence
  *   rows          : packed query rows per KV head = (H_q / H_kv) * N_q
- *   chunk_hint    : 0 = choose; otherwise the target keys per range (rounded to a multiple of 64)
+ *   num_sms       : SMs of the device, three CTA slots each; 0 = 148; a negative value is minus the number
+ *                   of CTA slots itself (a kernel configuration that fits two CTAs per SM: -2 * SMs)
+ *   chunk_hint    : 0 = choose (the cheaper of whole sequences and shrinking ranges under a list-scheduling
+ *                   estimate); otherwise the target keys per range (rounded to a multiple of 64)
  *   items         : host output, capacity max_items
  *   n_items       : output, number of ranges (each range owns one partial-result slot)
  *   max_range_keys: output, the longest range in keys */
