@@ -844,9 +844,11 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     // with the shortest estimated launch.
     build(false, 1, v, max_range);
     int64_t best = estimate(v);
+    // no plan beats (all work + one start-up per unit) / slots: stop when whole sequences are within 6 % of it
+    const int64_t lower = (work + 500 * units) / std::max<int64_t>(slots, 1);
     std::vector<fa_decode_item> alt;
     int alt_range = 0;
-    for (int cand = 0; cand < 3; ++cand) {
+    for (int cand = 0; cand < 3 && best * 100 > lower * 106; ++cand) {
       if (cand == 0) build(true, 1, alt, alt_range);
       else build(false, cand + 1, alt, alt_range);
       const int64_t t = estimate(alt);
