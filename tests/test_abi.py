@@ -65,3 +65,51 @@ def test_planner_on_host():
     # invalid arguments are reported, not crashed on
     assert lib.fa_decode_plan(None, -5, 1, 1, 1, 16, 148, 0, C.cast(items, C.c_void_p), cap, C.byref(n), C.byref(mr)) == 1
     assert b"negative" in lib.fa_last_error()
+
+
+def _plan(lib, lens, n_k, H_kv, rows, page, sms, hint=0):
+    from fa_kernels import _lib
+    B = len(lens) if lens is not None else 4
+    arr = (C.c_int32 * B)(*lens) if lens is not None else None
+    ptr = C.cast(arr, C.c_void_p) if arr is not None else None
+    cap = lib.fa_decode_plan_max_items(ptr, n_k, B, page)
+    items = (_lib.DecodeItem * cap)()
+    n, mr = C.c_int(), C.c_int()
+    assert lib.fa_decode_plan(ptr, n_k, B, H_kv, rows, page, sms, hint, C.cast(items, C.c_void_p), cap,
+                              C.byref(n), C.byref(mr)) == 0
+    assert n.value <= cap
+    return [items[i] for i in range(n.value)], mr.value
+
+
+def test_planner_candidates_cover_every_sequence_once():
+    """The planner picks between whole sequences, two or three equal ranges and shrinking ranges; whatever
+    it picks, the ranges of a sequence tile [0, len) in split order, start on multiples of 64, own
+    consecutive partial-result slots, and come longest first.  Shapes: one wave of whole sequences, a
+    partly filled second wave (equal splits), few long sequences (shrinking ranges), a single head, and
+    slot counts given exactly (negative num_sms)."""
+    from fa_kernels import _lib
+    lib = _lib.load()
+    shapes = [
+        ([8192] * 37, 0, 8, 4, 16, -296), ([8192] * 45, 0, 8, 4, 16, -296), ([8192] * 80, 0, 8, 4, 16, -296),
+        (None, 1048576, 8, 4, 64, 148), ([131072], 0, 1, 1, 256, -296), ([5, 70000, 0, 64, 4097], 0, 2, 16, 16, 148),
+        ([300] * 1000, 0, 8, 4, 16, 148),
+    ]
+    kinds = set()
+    for lens, n_k, H_kv, rows, page, sms in shapes:
+        got, mr = _plan(lib, lens, n_k, H_kv, rows, page, sms)
+        seq = lens if lens is not None else [n_k] * 4
+        for b, ln in enumerate(seq):
+            mine = sorted((it.split, it.k_begin, it.k_end, it.n_split, it.slot_base) for it in got if it.b == b)
+            assert len(mine) == mine[0][3] and [m[0] for m in mine] == list(range(len(mine)))
+            assert mine[0][1] == 0 and mine[-1][2] == ln
+            assert all(mine[i][2] == mine[i + 1][1] for i in range(len(mine) - 1))
+            assert len({m[4] for m in mine}) == 1
+        sizes = [it.k_end - it.k_begin for it in got]
+        assert sizes == sorted(sizes, reverse=True) and max(sizes) == mr
+        assert all((it.k_begin % 64) == 0 for it in got)
+        per_seq = len(got) / len(seq)
+        kinds.add("whole" if per_seq == 1 else ("few" if per_seq <= 3 else "many"))
+    assert kinds == {"whole", "few", "many"}          # each kind of plan was chosen somewhere
+    # one full wave of equal sequences stays whole; a wave and a half is cut
+    assert len(_plan(lib, [8192] * 37, 0, 8, 4, 16, -296)[0]) == 37
+    assert len(_plan(lib, [8192] * 45, 0, 8, 4, 16, -296)[0]) > 45
