@@ -848,7 +848,8 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     const int64_t lower = (work + 500 * units) / std::max<int64_t>(slots, 1);
     std::vector<fa_decode_item> alt;
     int alt_range = 0;
-    for (int cand = 0; cand < 3 && best * 100 > lower * 106; ++cand) {
+    // shrinking ranges only pay when there are fewer units than slots; with more they are not tried
+    for (int cand = (units >= slots ? 1 : 0); cand < 3 && best * 100 > lower * 106; ++cand) {
       if (cand == 0) build(true, 1, alt, alt_range);
       else build(false, cand + 1, alt, alt_range);
       const int64_t t = estimate(alt);
