@@ -213,3 +213,54 @@ def test_append_token_by_token_equals_offline_build(fmt):
         np.testing.assert_array_equal(written, _np(P.paged_gather(ref_scales.unsqueeze(-1), bt, page, N)))
     if fmt == "nvfp4":
         np.testing.assert_array_equal(_np(extra["micro_pool"]), _np(ref_micro))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["e4m3", "nvfp4"])
+def test_mla_expand_latent_is_the_oracle_dequantisation_rounded_to_bf16(fmt):
+    """fa_mla_expand_latent writes bf16(dequantised latent) for exactly the tokens of the planned key
+    ranges, into the same pool rows, and leaves every other row of the destination alone."""
+    import ctypes as C
+    from fa_kernels import _decode, _lib
+    from fa_kernels._lib import FA_E4M3, FA_NVFP4
+    lib = _lib.load()
+    lib.fa_mla_expand_latent.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_int,
+                                         C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    dqk, page, lens = 576, 64, [130, 64, 1, 700]
+    B = len(lens)
+    rng = np.random.default_rng(7)
+    n_pages = [(n + page - 1) // page for n in lens]
+    num_blocks = sum(n_pages) + 3                               # three pages nobody references
+    perm = rng.permutation(num_blocks)
+    bt = np.zeros((B, max(n_pages)), dtype=np.int32)
+    cur = 0
+    for b, npg in enumerate(n_pages):
+        bt[b, :npg] = perm[cur:cur + npg]
+        cur += npg
+    x = (rng.standard_normal((num_blocks, page, 1, dqk)) * 0.1).astype(np.float32)
+    if fmt == "e4m3":
+        codes, scales = O.quantize_fp8_e4m3_per_token(x)
+        want = O.dequantize_fp8_e4m3(codes, scales[..., None])
+        pool, micro, tok, tensor_scale, dt = torch.from_numpy(codes).cuda(), None, torch.from_numpy(scales).cuda().contiguous(), 1.0, FA_E4M3
+    else:
+        packed, mic, sc = O.quantize_nvfp4(x)
+        want = O.dequantize_nvfp4(packed, mic, sc)
+        pool, micro, tok, tensor_scale, dt = torch.from_numpy(packed).cuda(), torch.from_numpy(mic).cuda(), None, sc, FA_NVFP4
+    want_bf16 = torch.from_numpy(np.ascontiguousarray(want)).to(torch.bfloat16)
+    dev = pool.device
+    items, n_items, _, _, _ = _decode.plan(tuple(lens), max(lens), B, 1, 16, page, dev, 128)
+    sentinel = torch.full((num_blocks, page, 1, dqk), -7.0, dtype=torch.bfloat16, device=dev)
+    out = sentinel.clone()
+    bt_d = torch.from_numpy(bt).cuda()
+    _lib.check(lib.fa_mla_expand_latent(pool.data_ptr(), dt, micro.data_ptr() if micro is not None else None,
+                                        tok.data_ptr() if tok is not None else None, float(tensor_scale), bt_d.data_ptr(),
+                                        bt.shape[1], num_blocks, page, items.data_ptr(), n_items, dqk, out.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream), "fa_mla_expand_latent")
+    torch.cuda.synchronize()
+    got = out.cpu()
+    touched = torch.zeros(num_blocks, page, dtype=torch.bool)
+    for b, n in enumerate(lens):
+        for t in range(n):
+            touched[bt[b, t // page], t % page] = True
+    assert torch.equal(got[touched].view(torch.int16), want_bf16[touched].view(torch.int16))
+    assert (got[~touched] == -7.0).all()
