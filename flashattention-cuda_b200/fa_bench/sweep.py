@@ -160,7 +160,7 @@ def run(a):
     return rows
 
 
-def main():
+def build_parser():
     p = argparse.ArgumentParser(description="Shape sweeps with the reference harness's command line.")
     p.add_argument("--backend", default="v8_gqa_ss")
     p.add_argument("--precision", default="fp16", choices=["fp32", "fp16", "bf16"])
@@ -182,7 +182,11 @@ def main():
     p.add_argument("--gqa-group", type=int, nargs="+", default=None, dest="gqa_groups")
     p.add_argument("--iters", type=int, default=15)
     p.add_argument("--json", default=None, help="also write the rows to this file")
-    a = p.parse_args()
+    return p
+
+
+def main():
+    a = build_parser().parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("no CUDA device; the sweep runs on the GPU")
     run(a)

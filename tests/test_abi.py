@@ -113,3 +113,20 @@ def test_planner_candidates_cover_every_sequence_once():
     # one full wave of equal sequences stays whole; a wave and a half is cut
     assert len(_plan(lib, [8192] * 37, 0, 8, 4, 16, -296)[0]) == 37
     assert len(_plan(lib, [8192] * 45, 0, 8, 4, 16, -296)[0]) > 45
+
+
+def test_sweep_takes_the_reference_harness_flags():
+    """fa_bench/sweep.py parses the command lines of the reference's bench/harness.py (:357-397) and
+    bench/regime.py (:292-320) unchanged."""
+    import importlib.util
+    path = os.path.join(REPO_ROOT, "flashattention-cuda_b200", "fa_bench", "sweep.py")
+    spec = importlib.util.spec_from_file_location("fa_sweep_cli", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    parse = mod.build_parser().parse_args
+    a = parse("--backend v8_gqa_ss --precision fp16 --batch-sweep 1 8 16 32 64 --page-size 256 --heads 32 --causal "
+              "--seq 8192 --dim 64 128 --decode --q-len 4 --gqa-group 1 2 4 8".split())
+    assert a.batch_sweep == [1, 8, 16, 32, 64] and a.gqa_groups == [1, 2, 4, 8] and a.decode and a.q_len == 4
+    assert a.seq == [8192] and a.dim == [64, 128] and a.page_size == 256 and a.causal
+    b = parse("--backend v12_mla_tc --mla-engine nvfp4 --kv-lens 8192 1048576 --h-kv 1 8 --max-ws-gb 8 --batch 2".split())
+    assert b.mla_engine == "nvfp4" and b.seq == [8192, 1048576] and b.h_kvs == [1, 8] and b.max_ws_gb == 8.0 and b.batch == 2
