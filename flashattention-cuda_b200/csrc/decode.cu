@@ -19,7 +19,6 @@
 
 #include <algorithm>
 #include <climits>
-#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
@@ -165,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, MINB) paged_decode_kernel(const Deco
     for (int i = tid; i <= pg1 - pg0 && i < p.bt_cap; i += kThreads) {
       int pid = (pg0 + i < p.n_logical) ? bt[pg0 + i] : -2;
       if ((unsigned)pid >= (unsigned)p.num_blocks) {   // never follow a bad table entry
-        if (p.status) atomicOr(p.status, 1);
+        if (p.status) atomicOr(p.status, FA_STATUS_BAD_BLOCK_TABLE);
         pid = -1;
       }
       s_bt[i] = pid;
@@ -705,14 +704,6 @@ __global__ void merge_partials_kernel(const float* __restrict__ o_parts, const f
 
 using namespace fa;
 
-static double env_double(const char* name, double dflt) {
-  const char* e = std::getenv(name);
-  if (!e || !*e) return dflt;
-  char* end = nullptr;
-  const double x = std::strtod(e, &end);
-  return end == e ? dflt : x;
-}
-
 extern "C" int fa_decode_plan_max_items(const int32_t* seq_lens_host, int n_k, int B, int page_size) {
   (void)page_size;
   int64_t total = 0;
@@ -742,7 +733,9 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
   // with many waves of whole sequences (>= 6 per slot) nothing is cut.
   // (Measured on B200: FP8 KV, B=4, 8 KV heads, 1 Mi-key contexts 1810 -> 1691 us against eight equal
   // waves; fp16, 8 KV heads, 8192-key contexts: 55 sequences 330 -> 294 us, 80 sequences 477 -> 457 us.)
-  const int64_t max_chunk = (int64_t)(kMaxPages - 1) * page_size / kTN * kTN;
+  // A range of n keys that starts anywhere inside a page touches at most n / page_size + 2 pages, and that
+  // is the number of block-table entries the kernel stages (at most kMaxPages).
+  const int64_t max_chunk = (int64_t)(kMaxPages - 2) * page_size / kTN * kTN;
   FA_CHECK_ARG(max_chunk >= kTN, "fa_decode_plan: page_size too small");
   const int64_t slots = num_sms > 0 ? (int64_t)num_sms * 3 : -(int64_t)num_sms;   // negative: the slot count itself
   const int64_t units = (int64_t)B * H_kv * row_tiles;
@@ -752,9 +745,8 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
   if (chunk_hint > 0) chunk = chunk_hint;
   chunk = std::min(round_tile(chunk), max_chunk);
 
-  static const double first_frac = env_double("FA_B200_PLAN_FIRST", 1.0);
-  static const int64_t floor_keys = (int64_t)env_double("FA_B200_PLAN_FLOOR", 1024.0);
-  static const double level_frac = std::min(std::max(env_double("FA_B200_PLAN_LEVEL", 0.5), 0.1), 0.95);
+  constexpr int64_t floor_keys = 1024;     // shortest range of the shrinking schedule
+  constexpr double level_frac = 0.5;       // share of what is left of a sequence that each level takes
   const int64_t share = std::max<int64_t>(work / slots, 1);
   // small jobs: let the floor fall to 256 keys so that there are still ranges for every slot
   const int64_t floor_chunk = std::min(std::min(round_tile(floor_keys), std::max<int64_t>(round_tile(share / 2), 256)), max_chunk);
@@ -776,7 +768,7 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
       for (int s2 = 1; s2 <= ns; ++s2) cuts.push_back(std::min<int64_t>((int64_t)s2 * cb, len));
     } else {
       int64_t pos = 0;
-      int64_t c = std::min(std::max(round_tile((int64_t)(share * first_frac)), floor_chunk), max_chunk);
+      int64_t c = std::min(std::max(round_tile(share), floor_chunk), max_chunk);
       while (pos < len) {
         const int64_t rem = len - pos;
         if (c <= floor_chunk || rem <= floor_chunk) {   // the rest in equal ranges of about the floor
@@ -877,10 +869,11 @@ extern "C" size_t fa_decode_workspace_bytes(int n_slots, int H_q, int N_q, int D
 extern "C" size_t fa_decode_counters_len(int B, int H_q, int H_kv, int N_q) {
   const int G = H_kv > 0 ? H_q / H_kv : 1;
   const int row_tiles = (G * N_q + kRowTile - 1) / kRowTile;
-  return (size_t)B * H_kv * row_tiles + 1;   // +1 status word
+  return (size_t)B * H_kv * row_tiles + 1;   // word 0 is the status word
 }
 
-extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
+// Every argument check of the decode entry points; nothing is enqueued before this has passed.
+static int decode_check(const fa_decode_args* a) {
   FA_CHECK_ARG(a != nullptr, "fa_paged_decode_fwd: null args");
   FA_CHECK_ARG(a->q && a->k_pool && a->v_pool && a->block_table && a->items && a->out,
                "fa_paged_decode_fwd: q, k_pool, v_pool, block_table, items, out must be non-null");
@@ -921,6 +914,19 @@ extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
   FA_CHECK_ARG(a->counters != nullptr, "counters must be non-null");
   if (a->counters_len < n_counters) return fail(FA_ERR_WORKSPACE, "counters hold %zu ints < %zu", a->counters_len, n_counters);
 
+  if (a->max_range_keys / a->page_size + 2 > kMaxPages)
+    return fail(FA_ERR_INVALID, "key range of %d keys spans more than %d pages", a->max_range_keys, kMaxPages);
+  (void)fmt;
+  return FA_OK;
+}
+
+extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
+  const int rc_check = decode_check(a);
+  if (rc_check != FA_OK) return rc_check;
+  const int fmt = a->kv_dtype == FA_F16 ? KV_F16 : a->kv_dtype == FA_BF16 ? KV_BF16 : a->kv_dtype == FA_E4M3 ? KV_E4M3 : KV_NVFP4;
+  const int G = a->H_q / a->H_kv;
+  const int M = G * a->N_q;
+  const int row_tiles = (M + kRowTile - 1) / kRowTile;
   DecodeParams p{};
   p.q = reinterpret_cast<const uint16_t*>(a->q);
   p.k_pool = reinterpret_cast<const uint8_t*>(a->k_pool);
@@ -934,12 +940,11 @@ extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
   p.items = a->items;
   p.out = a->out;
   p.lse = a->lse;
-  p.counters = a->counters;
-  p.status = p.counters + (n_counters - 1);
+  p.status = a->counters;          // word 0: sticky error flags; the arrival counters follow
+  p.counters = a->counters + 1;
   p.part_o = reinterpret_cast<float*>(a->workspace);
   p.part_lse = p.part_o + (size_t)a->n_slots * a->H_q * a->N_q * a->D;
   p.bt_cap = a->max_range_keys / a->page_size + 2;
-  if (p.bt_cap > kMaxPages) return fail(FA_ERR_INVALID, "key range of %d keys spans more than %d pages", a->max_range_keys, kMaxPages);
   p.k_scale = a->k_scale;
   p.v_scale = a->v_scale;
   p.softmax_scale = a->softmax_scale;
@@ -982,48 +987,79 @@ extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
 }
 
 // ---- decode without any caller-supplied or allocated scratch ---------------------------------------
-// Scratch of fa_paged_decode_fwd_static: the first kStaticCounterWords int32 words are the arrival
-// counters, the rest holds the partial results of split sequences.  The array lives in the library's
-// device image, so every GPU that loads the library carries these bytes until the process exits.
+// Scratch of fa_paged_decode_fwd_static: word 0 is the status word (kept across calls until it is read with
+// fa_paged_decode_static_status), the next kStaticUnits int32 words are the arrival counters, and the
+// partial results of split sequences start at kStaticHeaderBytes.  The array lives in the library's device
+// image, so every GPU that loads the library carries these bytes until the process exits.
 namespace {
-constexpr size_t kStaticCounterWords = 16384;
+constexpr size_t kStaticUnits = 16384;                                  // (sequence, KV head, row tile) units per call
+constexpr size_t kStaticHeaderBytes = (kStaticUnits + 64) * sizeof(int32_t);
 constexpr size_t kStaticScratchBytes = FA_DECODE_STATIC_SCRATCH_BYTES;
+static_assert(kStaticHeaderBytes % 256 == 0 && kStaticHeaderBytes < kStaticScratchBytes, "static scratch layout");
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 constexpr int kMaxDevices = 64;
 unsigned char* g_static_scratch_ptr[kMaxDevices] = {nullptr};   // device address per device ordinal
-}  // namespace
 
-extern "C" int fa_paged_decode_fwd_static(const fa_decode_args* a) {
-  FA_CHECK_ARG(a != nullptr, "fa_paged_decode_fwd_static: null args");
+// Device address of the array on the current device: in host code the array's name is only a handle, the
+// address has to be asked for, once per device, with that device current.
+int static_scratch(unsigned char** out) {
   int dev = 0;
   FA_CUDA_OK(cudaGetDevice(&dev));
   FA_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "device ordinal %d out of range", dev);
   if (g_static_scratch_ptr[dev] == nullptr) {
-    // In host code the array's name is only a handle; the device address has to be asked for, once
-    // per device, with that device current.
     void* ptr = nullptr;
     FA_CUDA_OK(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
     g_static_scratch_ptr[dev] = static_cast<unsigned char*>(ptr);
   }
-  const size_t n_counters = fa_decode_counters_len(a->B, a->H_q, a->H_kv, a->N_q);
-  if (n_counters > kStaticCounterWords)
+  *out = g_static_scratch_ptr[dev];
+  return FA_OK;
+}
+}  // namespace
+
+extern "C" int fa_paged_decode_fwd_static(const fa_decode_args* a) {
+  FA_CHECK_ARG(a != nullptr, "fa_paged_decode_fwd_static: null args");
+  // the cheap shape checks come first, so that a rejected call has touched nothing on the device
+  FA_CHECK_ARG(a->B >= 1 && a->H_q >= 1 && a->H_kv >= 1 && a->N_q >= 1, "fa_paged_decode_fwd_static: bad B/H/N_q");
+  FA_CHECK_ARG(a->H_q % a->H_kv == 0, "H_q must be a positive multiple of H_kv; got H_q=%d H_kv=%d", a->H_q, a->H_kv);
+  if (a->D != 64 && a->D != 128) return fail(FA_ERR_UNSUPPORTED, "paged decode supports head_dim 64 or 128 (got %d)", a->D);
+  FA_CHECK_ARG(a->n_items >= 1 && (a->n_slots == 0 || a->n_slots == a->n_items), "n_slots must be 0 or n_items >= 1");
+  const size_t n_units = fa_decode_counters_len(a->B, a->H_q, a->H_kv, a->N_q) - 1;
+  if (n_units > kStaticUnits)
     return fail(FA_ERR_WORKSPACE,
-                "fa_paged_decode_fwd_static: %zu (sequence, head, row tile) counters exceed the built-in %zu; "
-                "use fa_paged_decode_fwd with caller scratch", n_counters, kStaticCounterWords);
-  const size_t part_cap = kStaticScratchBytes - kStaticCounterWords * sizeof(int32_t);
+                "fa_paged_decode_fwd_static: %zu (sequence, head, row tile) units exceed the built-in %zu; "
+                "use fa_paged_decode_fwd with caller scratch", n_units, kStaticUnits);
+  const size_t part_cap = kStaticScratchBytes - kStaticHeaderBytes;
   const size_t part_need = fa_decode_workspace_bytes(a->n_slots, a->H_q, a->N_q, a->D);
   if (part_need > part_cap)
     return fail(FA_ERR_WORKSPACE,
                 "fa_paged_decode_fwd_static: partial results need %zu B, the built-in scratch holds %zu B; "
                 "use fa_paged_decode_fwd with caller scratch", part_need, part_cap);
+  unsigned char* base = nullptr;
+  const int rc = static_scratch(&base);
+  if (rc != FA_OK) return rc;
   fa_decode_args b = *a;
-  b.counters = reinterpret_cast<int32_t*>(g_static_scratch_ptr[dev]);
-  b.counters_len = kStaticCounterWords;
-  b.workspace = g_static_scratch_ptr[dev] + kStaticCounterWords * sizeof(int32_t);
+  b.counters = reinterpret_cast<int32_t*>(base);
+  b.counters_len = kStaticUnits + 1;
+  b.workspace = base + kStaticHeaderBytes;
   b.workspace_bytes = part_cap;
-  // The array keeps whatever the previous call left; the counters have to start at zero.
-  FA_CUDA_OK(cudaMemsetAsync(b.counters, 0, n_counters * sizeof(int32_t), reinterpret_cast<cudaStream_t>(a->stream)));
+  const int rc_check = decode_check(&b);
+  if (rc_check != FA_OK) return rc_check;
+  // The array keeps whatever the previous call left; the arrival counters have to start at zero (an earlier
+  // call that ended in an error may have left some behind).  The status word is not cleared here.
+  FA_CUDA_OK(cudaMemsetAsync(b.counters + 1, 0, n_units * sizeof(int32_t), reinterpret_cast<cudaStream_t>(a->stream)));
   return fa_paged_decode_fwd(&b);
+}
+
+extern "C" int fa_paged_decode_static_status(int32_t* status_host, int clear, void* stream) {
+  FA_CHECK_ARG(status_host != nullptr, "fa_paged_decode_static_status: null pointer");
+  unsigned char* base = nullptr;
+  const int rc = static_scratch(&base);
+  if (rc != FA_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  FA_CUDA_OK(cudaMemcpyAsync(status_host, base, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  if (clear) FA_CUDA_OK(cudaMemsetAsync(base, 0, sizeof(int32_t), st));
+  FA_CUDA_OK(cudaStreamSynchronize(st));
+  return FA_OK;
 }
 
 extern "C" int fa_merge_partials(const float* o_parts, const float* lse_parts, int n_parts, int64_t rows, int D,
@@ -1049,6 +1085,20 @@ extern "C" int fa_paged_decode_host(const fa_decode_host_args* h) {
   FA_CHECK_ARG(h->max_items >= 1, "fa_paged_decode_host: max_items must be >= 1");
   fa_decode_args a = h->dev;
   FA_CHECK_ARG(a.B >= 1 && a.H_kv >= 1 && a.H_q >= 1 && a.N_q >= 1 && a.H_q % a.H_kv == 0, "fa_paged_decode_host: bad B/H/N_q");
+  FA_CHECK_ARG(a.page_size >= 1 && a.n_logical >= 1 && a.num_blocks >= 1, "fa_paged_decode_host: bad page_size / n_logical / num_blocks");
+  FA_CHECK_ARG(h->block_table_bytes >= (size_t)a.B * a.n_logical * sizeof(int32_t), "fa_paged_decode_host: block_table_host smaller than [B, n_logical]");
+  // The table is in host memory here, so a bad entry is refused before anything is enqueued (the kernel
+  // would mask the page and raise its status flag; the reference's host checks are of the same kind,
+  // kernels/v8_gqa_ss/gqa_ss_attention.cu:267-291).
+  for (int b = 0; b < a.B; ++b) {
+    const int len = h->seq_lens_host ? h->seq_lens_host[b] : h->n_k;
+    FA_CHECK_ARG(len >= 0, "fa_paged_decode_host: negative sequence length at b=%d", b);
+    const int64_t pages = ((int64_t)len + a.page_size - 1) / a.page_size;
+    FA_CHECK_ARG(pages <= a.n_logical, "fa_paged_decode_host: sequence %d needs %lld pages, the table has %d columns", b, (long long)pages, a.n_logical);
+    const int32_t* row = h->block_table_host + (size_t)b * a.n_logical;
+    for (int64_t j = 0; j < pages; ++j)
+      FA_CHECK_ARG((uint32_t)row[j] < (uint32_t)a.num_blocks, "fa_paged_decode_host: block_table[%d][%lld] = %d is outside [0, %d)", b, (long long)j, row[j], a.num_blocks);
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a.stream);
   FA_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a.q), h->q_host, h->q_bytes, cudaMemcpyHostToDevice, st));
   FA_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(a.block_table), h->block_table_host, h->block_table_bytes, cudaMemcpyHostToDevice, st));

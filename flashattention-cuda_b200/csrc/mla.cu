@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kMlaThreads, 1) mla_decode_kernel(const MlaPar
     for (int i = tid; i <= pg1 - pg0 && i < p.bt_cap; i += kMlaThreads) {
       int pid = (pg0 + i < p.n_logical) ? bt[pg0 + i] : -2;
       if ((unsigned)pid >= (unsigned)p.num_blocks) {
-        if (p.status) atomicOr(p.status, 1);
+        if (p.status) atomicOr(p.status, FA_STATUS_BAD_BLOCK_TABLE);
         pid = -1;
       }
       s_bt[i] = pid;
@@ -478,29 +478,26 @@ int launch_mla(const MlaParams& p, int n_items, int row_tiles, cudaStream_t st) 
 }  // namespace fa
 
 namespace fa {
-// tensor-core path (mla_tc.cu)
-bool mla_tc_applicable(const fa_mla_args* a, int max_pages);
+// CTA-pair tensor-core path (mla_pair.cu)
+bool mla_pair_applicable(const fa_mla_args* a);
 int mla_pair_max_pages();
-size_t mla_tc_workspace_bytes(int n_slots, int M);
-size_t mla_tc_counters_len(int B, int M);
-int launch_mla_tc(const fa_mla_args* a, cudaStream_t st);
-// CTA-pair tensor-core path (mla_pair.cu); same applicability and workspace as the path above
-int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStream_t st);
+size_t mla_pair_workspace_bytes(int n_slots, int M);
+size_t mla_pair_counters_len(int B, int M);
+int launch_mla_pair(const fa_mla_args* a, cudaStream_t st);
 }  // namespace fa
 
 using namespace fa;
 
 extern "C" size_t fa_mla_counters_len(int B, int H_q, int N_q) {
   const int row_tiles = (H_q * N_q + kMlaRows - 1) / kMlaRows;
-  return std::max((size_t)B * row_tiles + 1, mla_tc_counters_len(B, H_q * N_q));
+  return std::max((size_t)B * row_tiles + 1, mla_pair_counters_len(B, H_q * N_q));
 }
 
 extern "C" size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV) {
-  return std::max((size_t)n_slots * H_q * N_q * (DV + 1) * 4, mla_tc_workspace_bytes(n_slots, H_q * N_q));
+  return std::max((size_t)n_slots * H_q * N_q * (DV + 1) * 4, mla_pair_workspace_bytes(n_slots, H_q * N_q));
 }
 
-// Largest key range (in keys, a multiple of 64) one CTA of the tensor-core kernel can take at this page size.
-extern "C" int fa_mla_tc_max_range(int page_size) { return (126 * page_size) / 64 * 64; }
+// Largest key range (in keys, a multiple of 128) one CTA pair of the tensor-core kernel can take at this page size.
 extern "C" int fa_mla_pair_max_range(int page_size) {
   const long long keys = (long long)(mla_pair_max_pages() - 2) * page_size / 128 * 128;
   return (int)std::min<long long>(keys, 1 << 30);
@@ -540,17 +537,12 @@ extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   FA_CHECK_ARG(a->counters != nullptr, "counters must be non-null");
   if (a->counters_len < n_counters) return fail(FA_ERR_WORKSPACE, "counters hold %zu ints < %zu", a->counters_len, n_counters);
 
-  // bf16 (576, 512) latents on 64-token-aligned pages run on tcgen05 unless FA_B200_MLA_TC=0
-  static const bool tc_enabled = [] { const char* e = getenv("FA_B200_MLA_TC"); return !(e && e[0] == '0'); }();
-  // the CTA-pair kernel (cta_group::2) unless FA_B200_MLA_PAIR=0 or engine_hint 3 asks for the single-CTA one
-  static const bool pair_enabled = [] { const char* e = getenv("FA_B200_MLA_PAIR"); return !(e && e[0] == '0'); }();
-  const bool want_pair = pair_enabled && a->engine_hint != 3;
-  if (tc_enabled && a->engine_hint != 2 && mla_tc_applicable(a, want_pair ? mla_pair_max_pages() : 0)) {
-    if (a->workspace_bytes < mla_tc_workspace_bytes(a->n_slots, M))
-      return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, mla_tc_workspace_bytes(a->n_slots, M));
-    if (want_pair)
-      return launch_mla_pair(a, mla_tc_counters_len(a->B, M) - 1, reinterpret_cast<cudaStream_t>(a->stream));
-    return launch_mla_tc(a, reinterpret_cast<cudaStream_t>(a->stream));
+  // bf16 (576, 512) latents on power-of-two pages >= 64 run on the CTA-pair tcgen05 kernel unless the caller
+  // asks for the fused mma.sync kernel (engine_hint 2) or a key range is too long for it
+  if (a->engine_hint != 2 && mla_pair_applicable(a)) {
+    if (a->workspace_bytes < mla_pair_workspace_bytes(a->n_slots, M))
+      return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, mla_pair_workspace_bytes(a->n_slots, M));
+    return launch_mla_pair(a, reinterpret_cast<cudaStream_t>(a->stream));
   }
 
   MlaParams p{};
@@ -565,8 +557,8 @@ extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   p.lse = a->lse;
   p.part_o = reinterpret_cast<float*>(a->workspace);
   p.part_lse = p.part_o + (size_t)a->n_slots * a->H_q * a->N_q * a->DV;
-  p.counters = a->counters;
-  p.status = a->counters + (n_counters - 1);
+  p.status = a->counters;          // word 0: sticky error flags; the arrival counters follow
+  p.counters = a->counters + 1;
   p.scale_l = a->l_scale;
   p.softmax_scale = a->softmax_scale;
   p.n_logical = a->n_logical;

@@ -31,7 +31,6 @@
 // tensor-core backend kernels/v12_mla_tc/mla_tc_attention.cu:94-139.
 
 #include <climits>
-#include <cstdlib>
 
 #include "sm100.cuh"
 
@@ -129,13 +128,6 @@ __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[3
 }
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
-#ifdef FA_PAIR_TRACE
-__device__ long long g_pair_trace[3][256][8];
-#define PAIR_TRACE(who, j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 256) g_pair_trace[who][j][slot] = clock64(); } while (0)
-#else
-#define PAIR_TRACE(who, j, slot) do { } while (0)
-#endif
-
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_l, const MlaPairParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -207,7 +199,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int i = threadIdx.x; i <= pg1 - pg0 && i < kPMaxPages; i += kPThreads) {
       int pid = (pg0 + i < p.n_logical) ? bt[pg0 + i] : -2;
       if ((unsigned)pid >= (unsigned)p.num_blocks) {
-        if (p.status) atomicOr(p.status, 1);
+        if (p.status) atomicOr(p.status, FA_STATUS_BAD_BLOCK_TABLE);
         pid = 0;                     // never follow a bad entry: read block 0 instead and flag it
       }
       s_bt[i] = pid;
@@ -240,7 +232,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // by the second half; the scores start on blocks 0..3
         const int tok_own = token_of(k_begin + j * 128 + 64 * (int)rank);
         if (j >= 2 && !mbar_wait(bar(T_FREEA + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
-        PAIR_TRACE(0, j, 0);
         const uint32_t xa_full0 = map_to_cta(bar(X_FULL + bf), 0), xb_full0 = map_to_cta(bar(X_FULLB + bf), 0);
         if (rank == 0) mbar_expect_tx(bar(X_FULL + bf), 2 * 4 * kPBlk);
         for (int d = 0; d < 4; ++d) tma_pair_2d(smem_u32(sT + (bf * 9 + d) * kPBlk), &map_l, d * 64, tok_own, xa_full0);
@@ -255,16 +246,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
     }
-#ifdef FA_PAIR_TRACE
-    if (lane == 1 && rank == 0) {      // when do the loads land?
-      for (int j = 0; j < n_tiles; ++j) {
-        if (!mbar_wait(bar(X_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL)) break;
-        PAIR_TRACE(0, j, 2);
-        if (!mbar_wait(bar(R_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, P2_ERR_Y_FULL)) break;
-        PAIR_TRACE(0, j, 3);
-      }
-    }
-#endif
   } else if (warp == 6) {
     if (lane == 0 && n_tiles > 0) {
       // ------------------------------------------------- TMA producer of the peer's keys (both CTAs)
@@ -274,7 +255,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int j = 0; j < n_tiles; ++j) {
         const int bf = j & 1;
         if (!mbar_wait(bar(S_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_S_FULL)) break;
-        PAIR_TRACE(0, j, 1);
         const uint32_t r_full0 = map_to_cta(bar(R_FULL + bf), 0);
         if (rank == 0) mbar_expect_tx(bar(R_FULL + bf), 2 * 4 * kPBlk);
         const int tok_peer = token_of(k_begin + j * 128 + 64 * (1 - (int)rank));
@@ -297,7 +277,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (j >= 2) ok = mbar_wait(bar(P_READY + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_P_READY);
         if (ok) ok = mbar_wait(bar(X_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
-        PAIR_TRACE(1, j, 0);
         tc_fence_after();
         const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), d_s = tm_s + 64 * bf;
 #pragma unroll
@@ -313,7 +292,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                   smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
         }
         mma2_commit_both(bar(S_FULL + bf));
-        PAIR_TRACE(1, j, 1);
       }
     }
   } else if (warp == 7) {
@@ -333,7 +311,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         ok = mbar_wait(bar(P_READY + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_P_READY);
         if (!ok) break;
-        PAIR_TRACE(1, j, 3);
         tc_fence_after();
         const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), p_base = smem_u32(sP + bf * 2 * kPBlk);
 #pragma unroll
@@ -347,7 +324,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
         }
-        PAIR_TRACE(1, j, 4);
       }
     }
   }
@@ -389,13 +365,11 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int bf = j & 1;
       ok = mbar_wait(bar(S_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_S_FULL);
       if (!ok) break;
-      if (L == 0) PAIR_TRACE(2, j, 0);
       tc_fence_after();
       float s[64];
       tmem_ld32(tm_s + 64 * bf + lane_base, *reinterpret_cast<float(*)[32]>(&s[0]));
       tmem_ld32(tm_s + 64 * bf + lane_base + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
       tmem_wait_ld();
-      if (L == 0) PAIR_TRACE(2, j, 1);
       const int k0 = k_begin + j * 128;
       const int k0h = k0 + 64 * g;
       if (k0 + 127 > tile_limit) {
@@ -429,7 +403,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         sum1 += s[c + 1];
       }
       l_run = l_run * alpha + (sum0 + sum1);
-      if (L == 0) PAIR_TRACE(2, j, 2);
       // O may only be rescaled between two P V: this tile's is not issued before P arrives, the previous
       // one has to be waited for (rare: the maximum seldom rises by 2^8 after the first tiles)
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
@@ -447,7 +420,6 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         tmem_wait_st();
       }
-      if (L == 0) PAIR_TRACE(2, j, 3);
       // this thread's 64 probabilities -> row `row` of P block g (128 bytes, 16-byte chunks swizzled by row)
       {
         uint8_t* prow = sP + (bf * 2 + g) * kPBlk + row * 128;
@@ -478,12 +450,9 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
-      if (L == 0) PAIR_TRACE(2, j, 5);
       fence_proxy_async();
-      if (L == 0) PAIR_TRACE(2, j, 6);
       tc_fence_before();
       mbar_arrive_peer(map_to_cta(bar(P_READY + bf), 0));
-      if (L == 0) PAIR_TRACE(2, j, 4);
     }
     if (ok && n_tiles > 0)
       ok = mbar_wait(bar(T_FREE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
@@ -535,7 +504,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
   }
-  if (it.n_split == 1 || *s_abort) return;
+  if (it.n_split == 1) return;
 
   // ---- the last CTA of this (sequence, row tile, row half) merges all key ranges ------------------------
   __threadfence();
@@ -546,6 +515,9 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (*s_ticket != it.n_split - 1) return;
   __threadfence();
   if (threadIdx.x == 0) p.counters[cidx] = 0;
+  // after a wait that gave up the ticket is still taken, so that the counters are zero again for the next
+  // launch, but there is nothing valid to merge (the status word tells the host)
+  if (*s_abort) return;
   constexpr int kU = 8;
   for (int idx = threadIdx.x; idx < rows_valid * (kPDV / 4); idx += kPThreads) {
     const int row = idx / (kPDV / 4), d4 = idx - row * (kPDV / 4);
@@ -595,7 +567,18 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 // Host side; called by fa_mla_decode_fwd (mla.cu) after validation when the tensor-core path applies.
 int mla_pair_max_pages() { return kPMaxPages; }
 
-int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStream_t st) {
+bool mla_pair_applicable(const fa_mla_args* a) {
+  if (a->latent_dtype != FA_BF16 || a->DQK != kPDQK || a->DV != kPDV) return false;
+  if (a->page_size % 64 != 0 || (a->page_size & (a->page_size - 1)) != 0) return false;
+  if (a->max_range_keys / a->page_size + 2 > kPMaxPages) return false;
+  if ((int64_t)a->B * a->H_q * a->N_q > INT_MAX || (int64_t)a->num_blocks * a->page_size > INT_MAX) return false;
+  return true;
+}
+
+size_t mla_pair_workspace_bytes(int n_slots, int M) { return (size_t)n_slots * M * (kPDV + 2) * 4; }
+size_t mla_pair_counters_len(int B, int M) { return (size_t)B * ((M + 127) / 128) * 2 + 1; }   // word 0: status
+
+int launch_mla_pair(const fa_mla_args* a, cudaStream_t st) {
   const int M = a->H_q * a->N_q;
   const int row_tiles = (M + 127) / 128;
   CUtensorMap tq, tl;
@@ -622,8 +605,8 @@ int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStre
   p.lse = a->lse;
   p.part_o = reinterpret_cast<float*>(a->workspace);
   p.part_lse = p.part_o + (size_t)a->n_slots * M * kPDV;
-  p.counters = a->counters;
-  p.status = a->counters + counters_status_index;
+  p.status = a->counters;          // word 0: sticky error flags; the arrival counters follow
+  p.counters = a->counters + 1;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f * a->l_scale;
   p.scale_l = a->l_scale;
   p.n_logical = a->n_logical;
@@ -647,16 +630,5 @@ int launch_mla_pair(const fa_mla_args* a, size_t counters_status_index, cudaStre
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }
-
-#ifdef FA_PAIR_TRACE
-extern "C" __attribute__((visibility("default"))) int fa_debug_pair_trace_clear() {
-  void* ptr = nullptr;
-  cudaGetSymbolAddress(&ptr, g_pair_trace);
-  return (int)cudaMemset(ptr, 0, sizeof(g_pair_trace));
-}
-extern "C" __attribute__((visibility("default"))) int fa_debug_pair_trace(long long* dst, int n) {
-  return (int)cudaMemcpyFromSymbol(dst, g_pair_trace, sizeof(long long) * (size_t)n);
-}
-#endif
 
 }  // namespace fa

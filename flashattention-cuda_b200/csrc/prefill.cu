@@ -1,20 +1,29 @@
-// Dense (causal) attention forward on tcgen05 tensor cores with TMEM accumulators, fed by TMA.
+// Dense (causal) attention forward: two 128-row query tiles per CTA that take turns on the tensor core
+// ("ping-pong"), probabilities handed to the second MMA through tensor memory.  TMA (3-D tensor maps over
+// [B*H, N, d], 64 x 128 boxes, 128-byte swizzle, zero fill past N) -> shared memory -> tcgen05.mma.kind::f16
+// with fp32 accumulators in TMEM.
 //
-// One CTA owns a 128-row query tile of one (batch, head) and walks the key/value tiles of 128 keys.
-// Warp roles (6 warps):
-//   warp 0      TMA producer: Q once, then K/V tiles into a 2-stage ring (3-D tensor maps over
-//               [B*H, N, d], 128-byte swizzle, out-of-range rows zero filled)
-//   warp 1      allocates TMEM, issues every tcgen05.mma (one elected lane):
-//               S_j = Q K_j^T (K-major operands from shared memory) into one of two S buffers in TMEM,
-//               O  += P_j V_j  (P from shared memory, V as an MN-major operand) into the O columns
-//   warps 2..5  softmax: thread r owns query row r — reads its S row from TMEM (tcgen05.ld), scales,
-//               masks, keeps the running max / sum, rescales its O row in TMEM when the max moved,
-//               writes P (fp16 / bf16) into swizzled shared memory for the second MMA, and at the end
-//               normalises and stores its O row
-// TMEM columns: O [0,128)  S0 [128,256)  S1 [256,384).
-// Behaviour follows the reference's dense entry point (fa_kernels/__init__.py:26-42 ->
-// kernels/v5_wmma/wmma_attention.cu:229-263): inputs in half precision, fp32 accumulation, optional
-// top-left causal mask (key j masked when j > i, wmma_attention.cu:159), default output fp32.
+// Warp roles (12 warps, three warpgroups):
+//   warpgroup 0   warp 0: TMA producer (both Q tiles once, then K/V tiles into a 2-stage ring)
+//                 warp 1: TMEM allocation + every tcgen05.mma; warps 2, 3 idle; registers released
+//   warpgroup 1   softmax / correction / epilogue of query tile 0 (thread r owns row r)
+//   warpgroup 2   the same for query tile 1
+// TMEM (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512).  P_i (fp16 / bf16, two keys
+// per 32-bit column) overwrites the first 64 columns of S_i and is read from there as the A operand
+// of O_i += P_i V (tcgen05.mma with A in tensor memory), so it never touches shared memory.
+// MMA order per key tile j:  PV_j(0)  QK_{j+1}(0)  PV_j(1)  QK_{j+1}(1): while one tile's softmax runs on the
+// CUDA cores, the tensor core works for the other tile.  MMAs of one thread execute in issue order,
+// which is what makes reusing S_i for P_i and then for S_i of the next key tile safe.
+// The running maximum is only raised (and O rescaled) when it grew by more than 2^8, which keeps
+// P <= 256 in half precision and makes TMEM round trips of O rare.
+//
+// fp16 inputs: the exponentials run two per MUFU operation (ex2.approx.f16x2 on the half-precision
+// pair of scale * s - m); P is needed in half precision for the second MMA anyway, so nothing is rounded
+// twice, and the row sum is taken over the rounded P (pairwise in half precision over 8 values, then fp32).
+// bf16 inputs keep fp32 exponentials (a bf16 exponent argument would be too coarse).
+//
+// Behaviour: the reference's dense entry point (fa_kernels/__init__.py:26-42,
+// kernels/v5_wmma/wmma_attention.cu:229-263).
 
 #include <cstdlib>
 
@@ -25,12 +34,9 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBM = 128;          // query rows per CTA
-constexpr int kBN = 128;          // keys per tile
-constexpr int kStages = 2;
-constexpr int kPrefillThreads = 192;
-constexpr uint32_t kTmemCols = 512;
-constexpr float kLog2eF = 1.4426950408889634f;
+constexpr int kP2Threads = 384;
+constexpr uint32_t kP2TmemCols = 512;
+constexpr float kRescaleThreshold = 8.f;     // log2 units
 
 struct PrefillParams {
   void* out;
@@ -41,37 +47,98 @@ struct PrefillParams {
   float scale_log2;
 };
 
-enum PrefillErr { ERR_Q = 11, ERR_KV_FULL = 12, ERR_KV_EMPTY = 13, ERR_S_FULL = 14, ERR_S_EMPTY = 15, ERR_P_FULL = 16,
-                  ERR_PV_DONE = 17 };
+enum { P2_ERR_Q = 21, P2_ERR_KV_FULL = 22, P2_ERR_KV_EMPTY = 23, P2_ERR_S_FULL = 24, P2_ERR_P_READY = 25, P2_ERR_O_DONE = 26 };
 
+template <int NREG>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
+template <int NREG>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
+
+// 32 packed columns (64 half-precision values) of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// ---- packed fp32 pairs (two fp32 lanes in one 64-bit register: fma / add issue once for two values) ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// (lo, hi) fp32 -> packed half2, round to nearest; +-inf and out-of-range values become +-inf
+__device__ __forceinline__ uint32_t cvt_h2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// 2^x of both halves in one MUFU operation (half-precision result)
+__device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
+  uint32_t r;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(x));
+  return r;
+}
+__device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 template <int D, bool BF16>
-__global__ void __launch_bounds__(kPrefillThreads, 1)
+__global__ void __launch_bounds__(kP2Threads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
-  constexpr int KB = D / 64;                     // 64-element (128-byte) blocks along d
-  constexpr int TILE_BYTES = 128 * D * 2;        // one 128-row tile of Q, K or V
-  constexpr int BLK_BYTES = 128 * 128;           // one [128 rows][64 elements] block
+                const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+  constexpr int KB = D / 64;
+  constexpr int TILE_BYTES = 128 * D * 2;
+  constexpr int BLK_BYTES = 128 * 128;
+  constexpr int STAGES = 2;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;                 // [stage]
-  uint8_t* sV = sK + kStages * TILE_BYTES;       // [stage]
-  uint8_t* sP = sV + kStages * TILE_BYTES;       // [2 key blocks][128 rows][64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * BLK_BYTES);
-  // barrier indices
-  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, S_EMPTY = 7, P_FULL = 9, PV_DONE = 10, NBARS = 11 };
+  uint8_t* sQ = smem;                                  // [2 query tiles]
+  uint8_t* sK = sQ + 2 * TILE_BYTES;                   // [stage]
+  uint8_t* sV = sK + STAGES * TILE_BYTES;              // [stage]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + STAGES * TILE_BYTES);
+  enum { Q_FULL = 0, KV_FULL = 1, KV_EMPTY = 3, S_FULL = 5, P_READY = 7, O_DONE = 9, NBARS = 11 };
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + NBARS);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qt = (p.N_q + kBM - 1) / kBM;
-  const int qt = n_qt - 1 - (int)blockIdx.x;     // heaviest (last) causal tiles first
+  const int wg = warp >> 2;
+  const int n_qt = (p.N_q + 255) / 256;
+  const int qt = n_qt - 1 - (int)blockIdx.x;          // heaviest causal tiles first
   const int bh = blockIdx.y;
-  const int q0 = qt * kBM;
-  int n_tiles = (p.N_k + kBN - 1) / kBN;
-  if (p.causal) n_tiles = min(n_tiles, (q0 + kBM - 1) / kBN + 1);
+  const int q0 = qt * 256;
+  const int n_all = (p.N_k + 127) / 128;
+  // key tiles each query tile needs (causal: up to the tile holding its last row)
+  int n_t[2];
+  n_t[0] = p.causal ? min(n_all, (q0 + 127) / 128 + 1) : n_all;
+  n_t[1] = p.causal ? min(n_all, (q0 + 255) / 128 + 1) : n_all;
+  if (q0 + 128 >= p.N_q) n_t[1] = 0;                   // second query tile entirely out of range
+  const int n_max = max(n_t[0], n_t[1]);
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
@@ -80,177 +147,203 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(bar(KV_FULL + s), 1);
       mbar_init(bar(KV_EMPTY + s), 1);
       mbar_init(bar(S_FULL + s), 1);
-      mbar_init(bar(S_EMPTY + s), 128);
+      mbar_init(bar(P_READY + s), 128);
+      mbar_init(bar(O_DONE + s), 1);
     }
-    mbar_init(bar(P_FULL), 128);
-    mbar_init(bar(PV_DONE), 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_alloc(smem_u32(s_tmem), kP2TmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t tm_o = tmem, tm_s0 = tmem + 128;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
-      for (int kb = 0; kb < KB; ++kb) tma_load_3d(smem_u32(sQ + kb * BLK_BYTES), &tm_q, kb * 64, q0, bh, bar(Q_FULL));
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % kStages;
-        if (j >= kStages && !mbar_wait(bar(KV_EMPTY + s), ((j / kStages) - 1) & 1, s_abort, p.status, ERR_KV_EMPTY)) break;
+  if (wg == 0) {
+    setmaxnreg_dec<40>();   // 128 x 40 + 256 x 232 = 384 x 168, the register total the CTA was launched with
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      mbar_expect_tx(bar(Q_FULL), 2 * TILE_BYTES);
+      for (int i = 0; i < 2; ++i)
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_3d(smem_u32(sQ + i * TILE_BYTES + kb * BLK_BYTES), &tm_q, kb * 64, q0 + i * 128, bh, bar(Q_FULL));
+      for (int j = 0; j < n_max; ++j) {
+        const int s = j % STAGES;
+        if (j >= STAGES && !mbar_wait(bar(KV_EMPTY + s), ((j / STAGES) - 1) & 1, s_abort, p.status, P2_ERR_KV_EMPTY)) break;
         mbar_expect_tx(bar(KV_FULL + s), 2 * TILE_BYTES);
         for (int kb = 0; kb < KB; ++kb) {
-          tma_load_3d(smem_u32(sK + s * TILE_BYTES + kb * BLK_BYTES), &tm_k, kb * 64, j * kBN, bh, bar(KV_FULL + s));
-          tma_load_3d(smem_u32(sV + s * TILE_BYTES + kb * BLK_BYTES), &tm_v, kb * 64, j * kBN, bh, bar(KV_FULL + s));
+          tma_load_3d(smem_u32(sK + s * TILE_BYTES + kb * BLK_BYTES), &tm_k, kb * 64, j * 128, bh, bar(KV_FULL + s));
+          tma_load_3d(smem_u32(sV + s * TILE_BYTES + kb * BLK_BYTES), &tm_v, kb * 64, j * 128, bh, bar(KV_FULL + s));
         }
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = idesc_f16(kBM, kBN, BF16, false, false);
-      constexpr uint32_t idesc_pv = idesc_f16(kBM, D, BF16, false, true);
-      auto issue_qk = [&](int j) {
-        const int s = j % kStages;
-        const uint32_t d_tmem = tm_s0 + (uint32_t)(j & 1) * 128;
+    } else if (warp == 1 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_qk = idesc_f16(128, 128, BF16, false, false);
+      constexpr uint32_t idesc_pv = idesc_f16(128, D, BF16, false, true);
+      auto issue_qk = [&](int i, int j) {
+        const int s = j % STAGES;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * BLK_BYTES + (k & 3) * 32;
-          mma_f16_ss(d_tmem, smem_desc_sw128(smem_u32(sQ) + off, 16, 1024),
+          mma_f16_ss(tmem + i * 128, smem_desc_sw128(smem_u32(sQ + i * TILE_BYTES) + off, 16, 1024),
                      smem_desc_sw128(smem_u32(sK + s * TILE_BYTES) + off, 16, 1024), idesc_qk, k > 0);
         }
-        mma_commit(bar(S_FULL + (j & 1)));
+        mma_commit(bar(S_FULL + i));
       };
-      bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, ERR_Q) &&
-                mbar_wait(bar(KV_FULL + 0), 0, s_abort, p.status, ERR_KV_FULL);
+      auto issue_pv = [&](int i, int j) {
+        const int s = j % STAGES;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // A = P_i in tensor memory: 16 keys = 8 packed columns; B = V [128 keys][D], MN-major
+          const uint64_t b_desc = smem_desc_sw128(smem_u32(sV + s * TILE_BYTES) + k * 2048, BLK_BYTES, 1024);
+          mma_f16_ts(tmem + 256 + i * 128, tmem + i * 128 + k * 8, b_desc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+      };
+      bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, P2_ERR_Q) &&
+                mbar_wait(bar(KV_FULL + 0), 0, s_abort, p.status, P2_ERR_KV_FULL);
       if (ok) {
         tc_fence_after();
-        issue_qk(0);
+        if (n_t[0] > 0) issue_qk(0, 0);
+        if (n_t[1] > 0) issue_qk(1, 0);
       }
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) {
-          const int s = (j + 1) % kStages;
-          ok = mbar_wait(bar(KV_FULL + s), ((j + 1) / kStages) & 1, s_abort, p.status, ERR_KV_FULL);
-          if (ok && j + 1 >= 2) ok = mbar_wait(bar(S_EMPTY + ((j + 1) & 1)), (((j + 1) >> 1) - 1) & 1, s_abort, p.status, ERR_S_EMPTY);
+      for (int j = 0; ok && j < n_max; ++j) {
+        const bool next = (j + 1 < n_max);
+        if (next) {
+          ok = mbar_wait(bar(KV_FULL + ((j + 1) % STAGES)), ((j + 1) / STAGES) & 1, s_abort, p.status, P2_ERR_KV_FULL);
           if (!ok) break;
-          tc_fence_after();
-          issue_qk(j + 1);
         }
-        ok = mbar_wait(bar(P_FULL), j & 1, s_abort, p.status, ERR_P_FULL);
-        if (!ok) break;
-        tc_fence_after();
-        const int s = j % kStages;
 #pragma unroll
-        for (int k = 0; k < kBN / 16; ++k) {
-          // A = P [128 rows][128 keys], K-major: key block k/4, 32 bytes per 16 keys inside the atom
-          const uint64_t a_desc = smem_desc_sw128(smem_u32(sP) + (k >> 2) * BLK_BYTES + (k & 3) * 32, 16, 1024);
-          // B = V [128 keys][D], MN-major: 16 keys = 2 atoms of 8 rows; d blocks of 64 are BLK_BYTES apart
-          const uint64_t b_desc = smem_desc_sw128(smem_u32(sV + s * TILE_BYTES) + k * 2048, BLK_BYTES, 1024);
-          mma_f16_ss(tm_o, a_desc, b_desc, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        for (int i = 0; i < 2; ++i) {
+          if (j < n_t[i]) {
+            ok = mbar_wait(bar(P_READY + i), j & 1, s_abort, p.status, P2_ERR_P_READY);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(i, j);
+            if (j + 1 == n_t[i]) mma_commit(bar(O_DONE + i));
+          }
+          if (i == 1) mma_commit(bar(KV_EMPTY + (j % STAGES)));
+          if (j + 1 < n_t[i]) issue_qk(i, j + 1);
         }
-        mma_commit(bar(PV_DONE));
-        mma_commit(bar(KV_EMPTY + s));
       }
     }
   } else {
+    setmaxnreg_inc<232>();
     // ------------------------------------------------------------------ softmax / correction / epilogue
-    const int quad = warp & 3;                       // TMEM lane quadrant this warp may touch
-    const int row = quad * 32 + lane;                // query row inside the tile
-    const int gi = q0 + row;                         // query index
+    const int i = wg - 1;                              // query tile of this warpgroup
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int gi = q0 + i * 128 + row;
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t tm_s = tmem + i * 128 + lane_base;
+    const uint32_t tm_o = tmem + 256 + i * 128 + lane_base;
+    const int nt = n_t[i];
+    float m_ref = -INFINITY, l_run = 0.f;              // m_ref: the maximum P and O are currently scaled by
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, ERR_S_FULL);
+    for (int j = 0; j < nt; ++j) {
+      ok = mbar_wait(bar(S_FULL + i), j & 1, s_abort, p.status, P2_ERR_S_FULL);
       if (!ok) break;
       tc_fence_after();
       float s[128];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tm_s0 + (uint32_t)(j & 1) * 128 + lane_base + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
+      for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
       tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(S_EMPTY + (j & 1)));
 
-      const int k0 = j * kBN;
-      const bool need_mask = (k0 + kBN > p.N_k) || (p.causal && k0 + kBN - 1 > q0);
-      float mx = -INFINITY;
+      const int k0 = j * 128;
+      const bool need_mask = (k0 + 128 > p.N_k) || (p.causal && k0 + 127 > q0 + i * 128);
+      // scores stay unscaled until the exponent: max commutes with the (positive) scale, and
+      // scale * s - m is one fused multiply-add per pair
       if (need_mask) {
-        const int limit = p.causal ? min(gi, p.N_k - 1) : p.N_k - 1;   // largest key this row may see
+        const int limit = p.causal ? min(gi, p.N_k - 1) : p.N_k - 1;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          s[c] = (k0 + c <= limit) ? s[c] * p.scale_log2 : -INFINITY;
-          mx = fmaxf(mx, s[c]);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          s[c] *= p.scale_log2;
-          mx = fmaxf(mx, s[c]);
-        }
+        for (int c = 0; c < 128; ++c)
+          if (k0 + c > limit) s[c] = -INFINITY;
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = fast_exp2(m_run - m_use);
-      float sum = 0.f;
+      // four independent chains each for the maximum and the sum: one warp per scheduler per query
+      // tile is all the parallelism there is, so dependent chains of 64 operations would set the pace
+      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 128; ++c) {
-        s[c] = fast_exp2(s[c] - m_use);
-        sum += s[c];
+      for (int c = 0; c < 128; c += 8) {
+        mxa = max3(mxa, s[c], s[c + 1]);
+        mxb = max3(mxb, s[c + 2], s[c + 3]);
+        mxc = max3(mxc, s[c + 4], s[c + 5]);
+        mxd = max3(mxd, s[c + 6], s[c + 7]);
+      }
+      float mx = fmaxf(fmaxf(mxa, mxb), fmaxf(mxc, mxd)) * p.scale_log2;
+      // raise the reference maximum only when it is more than 2^8 behind
+      const bool raise = (mx > m_ref + kRescaleThreshold) || (m_ref == -INFINITY && mx > -INFINITY);
+      float alpha = 1.f;
+      if (raise) {
+        alpha = fast_exp2(m_ref - mx);                 // m_ref = -inf -> 0
+        m_ref = mx;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_use, -m_use);
+      // P as packed half-precision pairs: register c holds keys 2c, 2c+1
+      uint32_t pk[64];
+      float sum;
+      if constexpr (BF16) {
+        uint64_t sums[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float x0, x1;
+          unpack2(fma2(pack2(s[2 * c], s[2 * c + 1]), sc2, nm2), x0, x1);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          sums[c & 3] = add2(sums[c & 3], pack2(e0, e1));
+          pk[c] = pack_bf2(e0, e1);
+        }
+        float sum_lo, sum_hi;
+        unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), sum_lo, sum_hi);
+        sum = sum_lo + sum_hi;
+      } else {
+        // two exponentials per MUFU operation; masked scores arrive as -inf and give +0
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          float x0, x1;
+          unpack2(fma2(pack2(s[2 * c], s[2 * c + 1]), sc2, nm2), x0, x1);
+          pk[c] = ex2_h2(cvt_h2(x0, x1));
+        }
+        // row sum of the rounded P: three pairwise levels in half precision (8 values <= 2^8 each, exact to
+        // 2^-11 relative per level), the remaining 16 partial sums in fp32
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int g8 = 0; g8 < 8; ++g8) {
+          const uint32_t a0 = hadd2_u32(pk[8 * g8 + 0], pk[8 * g8 + 1]), a1 = hadd2_u32(pk[8 * g8 + 2], pk[8 * g8 + 3]);
+          const uint32_t a2 = hadd2_u32(pk[8 * g8 + 4], pk[8 * g8 + 5]), a3 = hadd2_u32(pk[8 * g8 + 6], pk[8 * g8 + 7]);
+          const uint32_t w = hadd2_u32(hadd2_u32(a0, a1), hadd2_u32(a2, a3));
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+          acc[g8 & 1] += f.x;
+          acc[2 + (g8 & 1)] += f.y;
+        }
+        sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
       }
       l_run = l_run * alpha + sum;
-      const bool moved = (m_new != m_run);
-      m_run = m_new;
-
-      if (j > 0) {
-        ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, s_abort, p.status, ERR_PV_DONE);
-        if (!ok) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, moved)) {
+      // S_FULL of key tile j implies P V of key tile j-1 has finished (same issuing thread, in order),
+      // so O may be rescaled here
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            float o[32];
-            tmem_ld32(tm_o + lane_base + c * 32, o);
-            tmem_wait_ld();
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          tmem_ld32(tm_o + c * 32, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st32(tm_o + lane_base + c * 32, o);
-          }
-          tmem_wait_st();
+          for (int e = 0; e < 32; ++e) o[e] *= alpha;
+          tmem_st32(tm_o + c * 32, o);
         }
       }
-      // P row -> shared memory, K-major, 128-byte swizzle: chunk of 8 keys = 16 bytes
-      {
-        uint8_t* prow = sP + row * 128;
-#pragma unroll
-        for (int ch = 0; ch < 16; ++ch) {
-          uint4 v;
-          if constexpr (BF16) {
-            v.x = pack_bf2(s[ch * 8 + 0], s[ch * 8 + 1]); v.y = pack_bf2(s[ch * 8 + 2], s[ch * 8 + 3]);
-            v.z = pack_bf2(s[ch * 8 + 4], s[ch * 8 + 5]); v.w = pack_bf2(s[ch * 8 + 6], s[ch * 8 + 7]);
-          } else {
-            v.x = pack_h2(s[ch * 8 + 0], s[ch * 8 + 1]); v.y = pack_h2(s[ch * 8 + 2], s[ch * 8 + 3]);
-            v.z = pack_h2(s[ch * 8 + 4], s[ch * 8 + 5]); v.w = pack_h2(s[ch * 8 + 6], s[ch * 8 + 7]);
-          }
-          const int kb = ch >> 3, cc = ch & 7;
-          *reinterpret_cast<uint4*>(prow + kb * BLK_BYTES + ((cc ^ (row & 7)) << 4)) = v;
-        }
-      }
-      fence_proxy_async();
+      // P -> tensor memory over the first 64 columns of S_i: column c holds keys 2c, 2c+1
+      tmem_st32u(tm_s, *reinterpret_cast<const uint32_t(*)[32]>(&pk[0]));
+      tmem_st32u(tm_s + 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[32]));
+      tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(P_FULL));
+      mbar_arrive(bar(P_READY + i));
     }
-    // epilogue: wait for the last P V, normalise, store
-    if (ok) ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1, s_abort, p.status, ERR_PV_DONE);
-    if (ok) {
+    if (ok && nt > 0) ok = mbar_wait(bar(O_DONE + i), 0, s_abort, p.status, P2_ERR_O_DONE);
+    if (ok && nt > 0) {
       tc_fence_after();
       const float inv = (l_run > 0.f) ? 1.f / l_run : 0.f;
       const bool valid = gi < p.N_q;
@@ -258,67 +351,72 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
-        tmem_ld32(tm_o + lane_base + c * 32, o);
+        tmem_ld32(tm_o + c * 32, o);
         tmem_wait_ld();
         if (valid) {
           if (p.out_dtype == FA_F32) {
             float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow * D + c * 32);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+            for (int e = 0; e < 8; ++e)
+              dst[e] = make_float4(o[4 * e] * inv, o[4 * e + 1] * inv, o[4 * e + 2] * inv, o[4 * e + 3] * inv);
           } else {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + orow * D + c * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int e = 0; e < 4; ++e) {
               uint4 v;
               if (p.out_dtype == FA_BF16) {
-                v.x = pack_bf2(o[8 * i] * inv, o[8 * i + 1] * inv); v.y = pack_bf2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-                v.z = pack_bf2(o[8 * i + 4] * inv, o[8 * i + 5] * inv); v.w = pack_bf2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+                v.x = pack_bf2(o[8 * e] * inv, o[8 * e + 1] * inv); v.y = pack_bf2(o[8 * e + 2] * inv, o[8 * e + 3] * inv);
+                v.z = pack_bf2(o[8 * e + 4] * inv, o[8 * e + 5] * inv); v.w = pack_bf2(o[8 * e + 6] * inv, o[8 * e + 7] * inv);
               } else {
-                v.x = pack_h2(o[8 * i] * inv, o[8 * i + 1] * inv); v.y = pack_h2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-                v.z = pack_h2(o[8 * i + 4] * inv, o[8 * i + 5] * inv); v.w = pack_h2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+                v.x = pack_h2(o[8 * e] * inv, o[8 * e + 1] * inv); v.y = pack_h2(o[8 * e + 2] * inv, o[8 * e + 3] * inv);
+                v.z = pack_h2(o[8 * e + 4] * inv, o[8 * e + 5] * inv); v.w = pack_h2(o[8 * e + 6] * inv, o[8 * e + 7] * inv);
               }
-              dst[i] = v;
+              dst[e] = v;
             }
           }
         }
       }
-      if (valid && p.lse) p.lse[orow] = (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      if (valid && p.lse) p.lse[orow] = (l_run > 0.f) ? (m_ref + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
-  // ---- teardown: all roles meet, TMEM is released by the warp that allocated it --------------------
   tc_fence_before();
   __syncthreads();
   if (*s_abort) __nanosleep(200000);   // after a timed-out wait: give copies still in flight time to land
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, kTmemCols);
+    tmem_dealloc(tmem, kP2TmemCols);
   }
 }
 
+}  // namespace
+
 template <int D, bool BF16>
-int launch_prefill(const fa_dense_args* a, const PrefillParams& p, cudaStream_t st) {
+static int launch_prefill(const fa_dense_args* a, float scale_log2, cudaStream_t st) {
   CUtensorMap tq, tk, tv;
   const int dt = BF16 ? FA_BF16 : FA_F16;
   const uint64_t BH = (uint64_t)a->B * a->H;
+  const uint32_t box[3] = {64, 128, 1};
   {
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)a->N_q, BH};
     const uint64_t strides[2] = {(uint64_t)D * 2, (uint64_t)a->N_q * D * 2};
-    const uint32_t box[3] = {64, 128, 1};
     int rc = encode_tensor_map(&tq, dt, 3, const_cast<void*>(a->q), dims, strides, box, 1);
     if (rc) return rc;
   }
   {
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)a->N_k, BH};
     const uint64_t strides[2] = {(uint64_t)D * 2, (uint64_t)a->N_k * D * 2};
-    const uint32_t box[3] = {64, 128, 1};
     int rc = encode_tensor_map(&tk, dt, 3, const_cast<void*>(a->k), dims, strides, box, 1);
     if (rc) return rc;
     rc = encode_tensor_map(&tv, dt, 3, const_cast<void*>(a->v), dims, strides, box, 1);
     if (rc) return rc;
   }
+  PrefillParams p{};
+  p.out = a->out; p.lse = a->lse; p.status = a->status;
+  p.B = a->B; p.H = a->H; p.N_q = a->N_q; p.N_k = a->N_k;
+  p.causal = a->causal; p.out_dtype = a->out_dtype; p.scale_log2 = scale_log2;
   constexpr int TILE = 128 * D * 2;
-  constexpr int SMEM = TILE * (1 + 2 * kStages) + 2 * 128 * 128 + 256 + 1024;
+  constexpr int SMEM = TILE * 6 + 256 + 1024;
   auto kern = prefill_kernel<D, BF16>;
   static int configured_device = -1;
   int dev = 0;
@@ -327,18 +425,13 @@ int launch_prefill(const fa_dense_args* a, const PrefillParams& p, cudaStream_t 
     FA_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured_device = dev;
   }
-  dim3 grid((unsigned)((a->N_q + kBM - 1) / kBM), (unsigned)BH);
-  kern<<<grid, kPrefillThreads, SMEM, st>>>(tq, tk, tv, p);
+  dim3 grid((unsigned)((a->N_q + 255) / 256), (unsigned)BH);
+  kern<<<grid, kP2Threads, SMEM, st>>>(tq, tk, tv, p);
   FA_CUDA_OK(cudaGetLastError());
   return FA_OK;
 }
 
-}  // namespace
 }  // namespace fa
-
-namespace fa {
-int launch_prefill2(const fa_dense_args* a, float scale_log2, cudaStream_t st);   // prefill2.cu
-}
 
 using namespace fa;
 
@@ -352,18 +445,8 @@ extern "C" int fa_dense_fwd(const fa_dense_args* a) {
   FA_CHECK_ARG((((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->out) & 15) == 0,
                "fa_dense_fwd: q, k, v, out must be 16-byte aligned");
   if (a->D != 64 && a->D != 128) return fail(FA_ERR_UNSUPPORTED, "dense attention supports head_dim 64 or 128 (got %d)", a->D);
-  PrefillParams p{};
-  p.out = a->out;
-  p.lse = a->lse;
-  p.status = a->status;
-  p.B = a->B; p.H = a->H; p.N_q = a->N_q; p.N_k = a->N_k;
-  p.causal = a->causal; p.out_dtype = a->out_dtype;
-  p.scale_log2 = a->softmax_scale * kLog2eF;
+  const float scale_log2 = a->softmax_scale * 1.4426950408889634f;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
-  // Two generations of the kernel exist; the second (two query tiles per CTA, P through tensor memory)
-  // is the default, FA_B200_PREFILL_GEN=1 selects the first.
-  static const int gen = [] { const char* e = getenv("FA_B200_PREFILL_GEN"); return (e && e[0] == '1') ? 1 : 2; }();
-  if (gen == 2) return launch_prefill2(a, p.scale_log2, st);
-  if (a->D == 128) return a->dtype == FA_BF16 ? launch_prefill<128, true>(a, p, st) : launch_prefill<128, false>(a, p, st);
-  return a->dtype == FA_BF16 ? launch_prefill<64, true>(a, p, st) : launch_prefill<64, false>(a, p, st);
+  if (a->D == 128) return a->dtype == FA_BF16 ? launch_prefill<128, true>(a, scale_log2, st) : launch_prefill<128, false>(a, scale_log2, st);
+  return a->dtype == FA_BF16 ? launch_prefill<64, true>(a, scale_log2, st) : launch_prefill<64, false>(a, scale_log2, st);
 }

@@ -32,6 +32,31 @@ int device_sm_count() {
 
 extern "C" const char* fa_last_error(void) { return fa::last_error_buf(); }
 extern "C" int fa_version(void) { return 100; }
+extern "C" const char* fa_status_text(int status_word) {
+  static thread_local char buf[160];
+  if (status_word == 0) return "ok";
+  const int code = status_word & 0xffff;
+  const char* wait = "";
+  switch (code) {
+    case 0: break;
+    case 21: wait = "dense attention: wait for the Q tiles timed out"; break;
+    case 22: wait = "dense attention: wait for a K/V stage to fill timed out"; break;
+    case 23: wait = "dense attention: wait for a K/V stage to drain timed out"; break;
+    case 24: wait = "dense attention: wait for the scores timed out"; break;
+    case 25: wait = "dense attention: wait for P timed out"; break;
+    case 26: wait = "dense attention: wait for the last P V timed out"; break;
+    case 41: case 42: wait = "MLA pair kernel: wait for the query operand timed out"; break;
+    case 43: case 44: wait = "MLA pair kernel: wait on a score-operand tile buffer timed out"; break;
+    case 45: case 46: wait = "MLA pair kernel: wait on a value-operand tile buffer timed out"; break;
+    case 47: wait = "MLA pair kernel: wait for the scores timed out"; break;
+    case 48: wait = "MLA pair kernel: wait for P timed out"; break;
+    case 49: wait = "MLA pair kernel: wait for a P V batch timed out"; break;
+    default: wait = "a bounded device wait timed out"; break;
+  }
+  snprintf(buf, sizeof buf, "%s%s%s (status 0x%x)", wait, (code && (status_word & FA_STATUS_BAD_BLOCK_TABLE)) ? "; " : "",
+           (status_word & FA_STATUS_BAD_BLOCK_TABLE) ? "block-table entry outside [0, num_blocks)" : "", status_word);
+  return buf;
+}
 extern "C" int fa_device_sm_count(int* sm_count) {
   if (!sm_count) return fa::fail(FA_ERR_INVALID, "fa_device_sm_count: null pointer");
   const int n = fa::device_sm_count();

@@ -35,19 +35,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  `abort_flag` is a CTA-shared int; `status` a global error word (may be null).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_cycles(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                                 long long max_cycles) {
   if (*abort_flag) return false;
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > max_cycles) {
       *abort_flag = 1;
-      if (status) atomicCAS(status, 0, code);
+      if (status) {   // the first wait that gave up names the code; the block-table flag (bit 16) is kept beside it
+        const int old = atomicCAS(status, 0, code);
+        if (old == FA_STATUS_BAD_BLOCK_TABLE) atomicCAS(status, old, old | code);
+      }
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  return mbar_wait_cycles(bar, parity, abort_flag, status, code, kWaitCycles);
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }

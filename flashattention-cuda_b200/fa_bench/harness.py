@@ -1,12 +1,12 @@
 """Per-workload measurement rows for every kernel family (the role of the reference's
-`python -m bench.harness`, bench/harness.py:101-354: CUDA-event timing against a CPU/torch baseline
-with a roofline column).
+`python -m bench.harness`, bench/harness.py:101-354: CUDA-event timing with a roofline column).
 
-    python flashattention-cuda_b200/fa_bench/harness.py [--workloads a,b,...] [--iters N] [--cpu-seconds S]
+    python flashattention-cuda_b200/fa_bench/harness.py [--workloads a,b,...] [--iters N]
 
-One JSON line per workload: p50 / min microseconds, achieved GB/s or TFLOP/s, fraction of the measured
-peak (MEASURED_PEAKS.json at the repository root when present), and the reference's CPU path (torch
-SDPA through oracle/cpu_reference.py) timed on a bounded sample of the same inputs.
+One JSON line per workload: p10 / p50 / p90 / max milliseconds over CUDA-event samples (L2 flushed before
+every launch), the algorithmic work of one launch (fa_bench/roofline.py) and the achieved GB/s or TFLOP/s
+as a fraction of the measured peak (MEASURED_PEAKS.json at the repository root when present).  bench.py at
+the repository root puts the same rows into its `workloads` array and adds the CPU baseline.
 """
 
 from __future__ import annotations
@@ -20,123 +20,105 @@ import time
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 REPO = os.path.dirname(PKG)
-for p_ in (PKG, REPO):
-    if p_ not in sys.path:
-        sys.path.insert(0, p_)
+if PKG not in sys.path:
+    sys.path.insert(0, PKG)
 
 import torch  # noqa: E402
 
-ALL = ["paged_gqa_decode_fp16", "long_decode_fp8", "long_decode_nvfp4", "causal_prefill_fp16", "mla_decode_bf16",
-       "mla_decode_fp8"]
+ALL = ["paged_gqa_decode_fp16", "causal_prefill_fp16", "mla_decode_bf16", "mla_decode_fp8", "long_decode_fp8",
+       "long_decode_nvfp4"]
 
 
-def peaks():
-    path = os.path.join(REPO, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        d = json.load(open(path))
-        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
-    return 6650.0, 1590.0, "fallback"
-
-
-def cpu_sample(name, w, seconds):
-    """Time the reference CPU path on a bounded sample; returns (work_done, seconds, description)."""
-    from oracle import cpu_reference as R
-    t_used, work = 0.0, 0.0
+def build(name, device, *, batch=None, ctx=None, seq_lens=None, data_seed=None):
+    """Seeded inputs of one benchmark configuration and the call that runs its kernel once.
+    Returns {"step": callable, "work": roofline.Work, "config": dict, "w": the tensors}."""
+    from fa_bench import roofline, workloads
     if name == "paged_gqa_decode_fp16":
-        kp, vp, bt, q = w["k_pool"].cpu(), w["v_pool"].cpu(), w["block_table_host"], w["q"].float().cpu()
-        n_done = 0
-        for b, n in enumerate(w["seq_lens"]):
-            k = R.gather_dense(kp, bt[b], w["page_size"], n).float()
-            v = R.gather_dense(vp, bt[b], w["page_size"], n).float()
-            t0 = time.perf_counter()
-            R.sdpa_reference_gqa(q[b:b + 1], k, v)
-            t_used += time.perf_counter() - t0
-            work += n * 2 * kp.shape[2] * kp.shape[3] * 2
-            n_done += 1
-            if t_used > seconds:
-                break
-        return work, t_used, f"{n_done} sequences, fp32 SDPA on dense KV"
-    if name.startswith("long_decode"):
-        from fa_kernels import paged as P
-        n = 131072                                           # one (sequence, kv head) slice of 128K keys, scaled linearly
-        bt = w["block_table"][:1, : n // w["page_size"]].contiguous()
-        if name.endswith("fp8"):
-            k = P.dequantize_fp8_e4m3(P.paged_gather(w["k_pool"], bt, w["page_size"], n), P.paged_gather(w["k_scale"].unsqueeze(-1), bt, w["page_size"], n)[..., 0])
-            v = P.dequantize_fp8_e4m3(P.paged_gather(w["v_pool"], bt, w["page_size"], n), P.paged_gather(w["v_scale"].unsqueeze(-1), bt, w["page_size"], n)[..., 0])
-            per_tok = 2 * 8 * (128 + 4)
+        from fa_kernels import gqa_attention
+        w = workloads.paged_gqa_decode(device, batch=batch or 64, seq_lens=seq_lens, data_seed=data_seed)
+        step = lambda: gqa_attention(w["q"], w["k_pool"], w["v_pool"], w["block_table"], w["page_size"], w["seq_lens"],
+                                     out_dtype=torch.float16)
+        B = len(w["seq_lens"])
+        work = roofline.paged_decode(w["tokens"], H_q=32, H_kv=8, d=128, B=B,
+                                     table_entries=sum((n + 15) // 16 for n in w["seq_lens"]))
+        cfg = {"workload": name, "batch": B, "h_q": 32, "h_kv": 8, "d": 128, "page_size": 16,
+               "ctx": "uniform[1024,8192] seed 2", "kv_tokens": w["tokens"]}
+        dtype = "f16"
+    elif name == "causal_prefill_fp16":
+        from fa_kernels import attention
+        w = workloads.causal_prefill(device, batch=batch or 4)
+        step = lambda: attention(w["q"], w["k"], w["v"], causal=True, out_dtype=torch.float16)
+        B, H, N, d = w["q"].shape
+        work = roofline.dense_attention(B, H, N, N, d, causal=True)
+        cfg = {"workload": name, "batch": B, "heads": H, "n": N, "d": d, "seed": 1,
+               "flops_undiscounted": roofline.dense_attention_full_flops(B, H, N, N, d)}
+        dtype = "f16"
+    elif name in ("mla_decode_bf16", "mla_decode_fp8"):
+        from fa_kernels import mla_attention
+        bf = name.endswith("bf16")
+        w = workloads.mla_decode(device, batch=batch or 128, latent="bf16" if bf else "e4m3", seq_lens=seq_lens)
+        step = lambda: mla_attention(w["q"], w["l_pool"], None, w["block_table"], w["page_size"], w["seq_lens"],
+                                     w["kv_lora_rank"], w["scale_l"], out_dtype=torch.bfloat16 if bf else torch.float16)
+        B = len(w["seq_lens"])
+        work = roofline.mla_decode(w["tokens"], h_q=128, latent_format="bf16" if bf else "e4m3", per_token_scales=not bf, B=B)
+        cfg = {"workload": name, "batch": B, "h_q": 128, "dqk": 576, "dv": 512, "page_size": 64,
+               "ctx": "uniform[4096,32768] seed 5", "kv_tokens": w["tokens"]}
+        dtype = "bf16" if bf else "f16 over e4m3 latent"
+    elif name in ("long_decode_fp8", "long_decode_nvfp4"):
+        from fa_kernels import fp8_attention, nvfp4_attention
+        fp8 = name.endswith("fp8")
+        w = workloads.quantised_long_context_decode(device, fmt="e4m3" if fp8 else "nvfp4", batch=batch or 4, ctx=ctx or 1048576)
+        if fp8:
+            step = lambda: fp8_attention(w["q"], w["k_pool"], w["v_pool"], w["block_table"], w["page_size"], w["n_k"],
+                                         w["k_scale"], w["v_scale"], out_dtype=torch.float16)
         else:
-            k = P.dequantize_nvfp4(P.paged_gather(w["k_pool"], bt, w["page_size"], n), P.paged_gather(w["k_micro"], bt, w["page_size"], n), w["k_scale"])
-            v = P.dequantize_nvfp4(P.paged_gather(w["v_pool"], bt, w["page_size"], n), P.paged_gather(w["v_micro"], bt, w["page_size"], n), w["v_scale"])
-            per_tok = 2 * 8 * 72
-        k, v, q = k.cpu(), v.cpu(), w["q"][:1].float().cpu()
-        reps = 0
-        while t_used < seconds:
-            t0 = time.perf_counter()
-            R.sdpa_reference_gqa(q, k, v)
-            t_used += time.perf_counter() - t0
-            reps += 1
-        return reps * n * per_tok, t_used, f"{reps} passes over the first 131072 keys of sequence 0 (dequantised outside the timing)"
-    if name == "causal_prefill_fp16":
-        q, k, v = (w[x][:1, :2].float().cpu() for x in ("q", "k", "v"))
-        reps = 0
-        while t_used < seconds:
-            t0 = time.perf_counter()
-            R.sdpa_reference(q, k, v, causal=True)
-            t_used += time.perf_counter() - t0
-            reps += 1
-        n, d = q.shape[2], q.shape[3]
-        return reps * 2 * 2 * d * n * (n + 1), t_used, f"{reps} passes over 2 of {w['q'].shape[0] * w['q'].shape[1]} heads, fp32 SDPA"
-    if name.startswith("mla_decode"):
-        from fa_kernels import paged as P
-        n = min(w["seq_lens"][0], 8192)
-        bt = w["block_table"][:1].contiguous()
-        lat = P.paged_gather(w["l_pool"], bt, w["page_size"], n)
-        if name.endswith("fp8"):
-            lat = P.dequantize_fp8_e4m3(lat, P.paged_gather(w["scale_l"].unsqueeze(-1), bt, w["page_size"], n)[..., 0])
-        lat, q = lat.float().cpu(), w["q"][:1].float().cpu()
-        reps = 0
-        while t_used < seconds:
-            t0 = time.perf_counter()
-            R.sdpa_reference_mla_dequantised(q, lat, w["kv_lora_rank"])
-            t_used += time.perf_counter() - t0
-            reps += 1
-        return reps * 2 * q.shape[1] * (q.shape[3] + w["kv_lora_rank"]) * n, t_used, f"{reps} passes over the first {n} keys of sequence 0"
-    raise ValueError(name)
+            step = lambda: nvfp4_attention(w["q"], w["k_pool"], w["k_micro"], w["v_pool"], w["v_micro"], w["block_table"],
+                                           w["page_size"], w["n_k"], w["k_scale"], w["v_scale"], out_dtype=torch.float16)
+        B = w["q"].shape[0]
+        work = roofline.paged_decode(w["tokens"], H_q=32, H_kv=8, d=128, kv_format="e4m3" if fp8 else "nvfp4",
+                                     per_token_scales=fp8, B=B, table_entries=B * (w["n_k"] // 64))
+        cfg = {"workload": name, "batch": B, "h_q": 32, "h_kv": 8, "d": 128, "page_size": 64, "ctx": w["n_k"],
+               "kv_tokens": w["tokens"], "outlier_channels": "1 % x10"}
+        dtype = "f16 over " + ("e4m3" if fp8 else "nvfp4") + " KV"
+    else:
+        raise SystemExit(f"unknown workload {name!r}")
+    return {"step": step, "work": work, "config": cfg, "w": w, "dtype": dtype}
 
 
-def run(name, iters, cpu_seconds, ctx=None, batch=None):
-    from fa_bench import timing, workloads
-    from fa_bench.profile_case import make_step
-    dev = torch.device("cuda:0")
-    hbm, tflops, src = peaks()
-    holder = {}
-    orig = {}
-    # capture the workload dict that make_step builds (for the CPU sample) by wrapping the builders
-    for fn_name in ("paged_gqa_decode", "quantised_long_context_decode", "causal_prefill", "mla_decode"):
-        orig[fn_name] = getattr(workloads, fn_name)
+def captured_traffic(name, work):
+    """DRAM bytes per launch from the committed ncu captures (profiles/ncu_traffic.json: bytes per unit of
+    work measured on a capture of the same kernel, scaled by this launch's units), or None."""
+    path = os.path.join(REPO, "profiles", "ncu_traffic.json")
+    if not os.path.exists(path):
+        return None, None
+    with open(path) as f:
+        table = json.load(f)
+    e = table.get(name)
+    if not e:
+        return None, None
+    units = work.kv_bytes if e["per"] == "kv_byte" else work.flops
+    return e["dram_bytes_per_unit"] * units, e["source"]
 
-        def wrap(f):
-            def inner(*a, **k):
-                holder["w"] = f(*a, **k)
-                return holder["w"]
-            return inner
-        setattr(workloads, fn_name, wrap(orig[fn_name]))
-    try:
-        fn, work = make_step(name, dev, batch, ctx)
-    finally:
-        for k_, v_ in orig.items():
-            setattr(workloads, k_, v_)
-    t = timing.summary(timing.time_cuda(fn, warmup=3, iters=iters, device=dev))
-    tensor_bound = "prefill" in name or "mla" in name
-    achieved = work / (t["p50"] * 1e-3) / (1e12 if tensor_bound else 1e9)
-    peak = tflops if tensor_bound else hbm
-    row = {"workload": name, "p50_us": t["p50"] * 1e3, "min_us": t["min"] * 1e3, "algorithmic_work": work,
-           "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
-                        "unit": "TFLOP/s" if tensor_bound else "GB/s", "frac": achieved / peak, "peak_source": src}}
-    if cpu_seconds > 0:
-        done, secs, desc = cpu_sample(name, holder["w"], cpu_seconds)
-        row["cpu_baseline"] = {"value": done / secs / (1e12 if tensor_bound else 1e9), "unit": row["roofline"]["unit"],
-                               "cores": torch.get_num_threads(), "kind": "port", "sample": desc}
+
+def measure(name, device, *, iters=20, warmup=3, batch=None, ctx=None, hold_seconds=0.0, case=None):
+    """Time one workload's kernel: `iters` CUDA-event samples, L2 flushed and the GPU held busy before
+    each.  `hold_seconds` keeps launching afterwards so that a clock sampler sees the GPU under load;
+    `case` is a workload already built with `build`."""
+    from fa_bench import roofline, timing
+    case = case or build(name, device, batch=batch, ctx=ctx)
+    t = timing.summary(timing.time_cuda(case["step"], warmup=warmup, iters=iters, device=device))
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < hold_seconds:
+        case["step"]()
+        torch.cuda.synchronize(device)
+    peaks = roofline.measured_peaks()
+    roof = roofline.achieved(case["work"], t["p50"] * 1e-3, peaks)
+    traffic, src = captured_traffic(name, case["work"])
+    roof["traffic"] = traffic
+    if src:
+        roof["traffic_source"] = src
+    row = {"workload": name, "config": case["config"], "dtype": case["dtype"], "p50_ms": t["p50"], "p10_ms": t["p10"],
+           "p90_ms": t["p90"], "max_ms": t["max"], "mean_ms": t["mean"], "samples": t["n"], "roofline": roof}
     return row
 
 
@@ -144,12 +126,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workloads", default=",".join(ALL))
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--cpu-seconds", type=float, default=3.0)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--batch", type=int, default=None)
     args = ap.parse_args()
+    dev = torch.device("cuda:0")
     for name in args.workloads.split(","):
-        print(json.dumps(run(name, args.iters, args.cpu_seconds, args.ctx, args.batch)), flush=True)
+        print(json.dumps(measure(name, dev, iters=args.iters, batch=args.batch, ctx=args.ctx)), flush=True)
         torch.cuda.empty_cache()
 
 

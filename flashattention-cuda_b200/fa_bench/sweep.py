@@ -35,12 +35,9 @@ _MLA_DV = {576: 512, 160: 128, 96: 64}          # latent widths the MLA kernels 
 
 
 def _peaks():
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            d = json.load(f)
-        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
-    return 6650.0, 1590.0, "fallback"
+    from fa_bench import roofline
+    p = roofline.measured_peaks()
+    return p.hbm_gbs, p.tensor_tflops, p.source
 
 
 def _time(fn, iters):

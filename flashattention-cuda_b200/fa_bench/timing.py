@@ -33,8 +33,21 @@ def flush_l2(device) -> None:
     torch.sum(sweep, dim=0, keepdim=True, out=sink)
 
 
-def time_cuda(fn, *, warmup: int = 3, iters: int = 10, flush: bool = True, device=None):
-    """Run `fn` warmup + iters times; return the list of per-iteration milliseconds."""
+_SPIN_CYCLES = 600_000        # ~0.3 ms of a kernel that touches no memory
+
+
+def hold_gpu(device) -> None:
+    """Keep the stream busy for ~0.3 ms without touching the L2.  Enqueued after the flush and before the
+    start event, it gives the host time to enqueue the timed launch (Python argument handling, plan-cache
+    lookup, ctypes call) while the GPU is still working, so that the event window holds the kernel alone
+    and no host gap: the start event's timestamp is taken when the spin ends and the timed kernel is
+    already queued behind it."""
+    torch.cuda._sleep(_SPIN_CYCLES)
+
+
+def time_cuda(fn, *, warmup: int = 3, iters: int = 10, flush: bool = True, device=None, hold: bool = True):
+    """Run `fn` warmup + iters times; return the list of per-iteration milliseconds (CUDA events on the
+    current stream around each call, L2 flushed before it, host launch latency kept out of the window)."""
     device = device or torch.device("cuda", torch.cuda.current_device())
     for _ in range(warmup):
         if flush:
@@ -45,6 +58,8 @@ def time_cuda(fn, *, warmup: int = 3, iters: int = 10, flush: bool = True, devic
     for _ in range(iters):
         if flush:
             flush_l2(device)
+        if hold:
+            hold_gpu(device)
         start = torch.cuda.Event(enable_timing=True)
         end = torch.cuda.Event(enable_timing=True)
         start.record()
@@ -56,5 +71,11 @@ def time_cuda(fn, *, warmup: int = 3, iters: int = 10, flush: bool = True, devic
 
 
 def summary(times):
+    """Median with the spread: p10 / p50 / p90 / min / max / mean of a list of milliseconds."""
     s = sorted(times)
-    return {"p50": statistics.median(s), "min": s[0], "max": s[-1], "mean": sum(s) / len(s)}
+    n = len(s)
+
+    def pct(p):
+        return s[min(n - 1, max(0, int(round(p * (n - 1)))))]
+    return {"p50": statistics.median(s), "p10": pct(0.10), "p90": pct(0.90), "min": s[0], "max": s[-1],
+            "mean": sum(s) / n, "n": n}

@@ -40,4 +40,7 @@ def __getattr__(name):
     if name == "HostDecodeStep":
         from ._decode import HostDecodeStep
         return HostDecodeStep
+    if name in ("check_status", "read_status", "set_status_checks"):
+        from . import _status
+        return getattr(_status, name)
     raise AttributeError(f"module 'fa_kernels' has no attribute {name!r}")

@@ -12,7 +12,7 @@ import ctypes as C
 
 import torch
 
-from . import _lib
+from . import _lib, _status
 from ._lib import FA_BF16, FA_E4M3, FA_F16, FA_F32, FA_NVFP4
 
 _TORCH_TO_FA = {torch.float16: FA_F16, torch.bfloat16: FA_BF16, torch.float32: FA_F32}
@@ -42,8 +42,11 @@ def plan(seq_lens, n_k: int, B: int, H_kv: int, rows: int, page_size: int, devic
     """Return (items_device_tensor, n_items, n_slots, max_range_keys); cached per argument set.
 
     `seq_lens` is None (every sequence has n_k keys) or a tuple of B ints.  The planner counts three CTA
-    slots per SM; a kernel that fits fewer (`ctas_per_sm`) is planned for proportionally fewer SMs."""
-    key = (seq_lens, n_k, B, H_kv, rows, page_size, str(device), chunk_hint, ctas_per_sm)
+    slots per SM; a kernel that fits fewer (`ctas_per_sm`) is planned for proportionally fewer SMs.
+    The device copy is uploaded on the current stream, so the cache is per stream as well: a kernel on
+    another stream would have no dependency on that upload."""
+    key = (seq_lens, n_k, B, H_kv, rows, page_size, str(device), torch.cuda.current_stream(device).cuda_stream,
+           chunk_hint, ctas_per_sm)
     hit = _plan_cache.get(key)
     if hit is not None:
         return hit
@@ -95,13 +98,15 @@ def _staging(device, cap: int):
 
 def workspace(device, nbytes: int, n_counters: int):
     """(partials uint8 tensor, counters int32 tensor), one pair per (device, stream), grown
-    geometrically.  The counters are allocated zeroed and the kernel hands them back zeroed."""
+    geometrically.  The counters are allocated zeroed and the kernel hands them back zeroed; word 0 is
+    the device status word (see _status.py)."""
     key = (str(device), torch.cuda.current_stream(device).cuda_stream)
     ws, cnt = _workspace.get(key, (None, None))
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(int(nbytes * 1.5), 1 << 20), dtype=torch.uint8, device=device)
     if cnt is None or cnt.numel() < n_counters:
         cnt = torch.zeros(max(int(n_counters * 2), 1 << 14), dtype=torch.int32, device=device)
+        _status.register(cnt)
     _workspace[key] = (ws, cnt)
     return ws, cnt
 
@@ -230,6 +235,7 @@ def paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal=F
     a.variant = int(variant)
     with torch.cuda.device(dev):
         _lib.check(lib.fa_paged_decode_fwd(C.byref(a)), "fa_paged_decode_fwd")
+    _status.after_call(dev)
     return (out, lse) if return_lse else out
 
 
@@ -309,6 +315,7 @@ class HostDecodeStep:
         self.turn = 0
         self.ws = torch.empty(int(lib.fa_decode_workspace_bytes(self.max_items, H_q, N_q, d)), dtype=torch.uint8, device=dev)
         self.cnt = torch.zeros(int(lib.fa_decode_counters_len(B, H_q, H_kv, N_q)), dtype=torch.int32, device=dev)
+        _status.register(self.cnt)
         h = DecodeHostArgs()
         a = h.dev
         a.q, a.q_dtype = self.q_dev.data_ptr(), _TORCH_TO_FA[self.q_t]

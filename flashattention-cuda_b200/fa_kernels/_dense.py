@@ -9,11 +9,11 @@ import ctypes as C
 
 import torch
 
-from . import _lib
+from . import _lib, _status
 from ._lib import FA_BF16, FA_F16, FA_F32
 
 _TORCH_TO_FA = {torch.float16: FA_F16, torch.bfloat16: FA_BF16, torch.float32: FA_F32}
-_status: dict = {}
+_words: dict = {}
 
 
 class DenseArgs(C.Structure):
@@ -27,9 +27,10 @@ class DenseArgs(C.Structure):
 def status_word(device) -> torch.Tensor:
     """Device int that a kernel sets when one of its bounded pipeline waits gave up (0 = healthy)."""
     key = str(device)
-    if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status[key]
+    if key not in _words:
+        _words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status.register(_words[key])
+    return _words[key]
 
 
 def _require(cond, msg):
@@ -65,4 +66,5 @@ def dense_attention(q, k, v, scale, causal, *, out_dtype=None, return_lse=False)
     a.stream = torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):
         _lib.check(lib.fa_dense_fwd(C.byref(a)), "fa_dense_fwd")
+    _status.after_call(dev)
     return (out, lse) if return_lse else out

@@ -52,6 +52,8 @@ def _declare(lib):
     lib.fa_last_error.restype = C.c_char_p
     lib.fa_last_error.argtypes = []
     lib.fa_version.restype = C.c_int
+    lib.fa_status_text.restype = C.c_char_p
+    lib.fa_status_text.argtypes = [C.c_int]
     lib.fa_device_sm_count.argtypes = [C.POINTER(C.c_int)]
     lib.fa_decode_plan.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
@@ -73,6 +75,8 @@ _OPTIONAL: dict = {
     "fa_mla_decode_fwd": [C.c_void_p],
     "fa_dense_fwd": [C.c_void_p],
     "fa_paged_decode_fwd_static": [C.POINTER(DecodeArgs)],
+    "fa_paged_decode_static_status": [C.POINTER(C.c_int32), C.c_int, C.c_void_p],
+    "fa_selftest_bounded_wait": [C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p],
     "fa_quantize_fp8_e4m3": [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p],
     "fa_dequantize_fp8_e4m3": [C.c_void_p, C.c_int64, C.c_float, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p],
     "fa_quantize_nvfp4": [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p],

@@ -11,7 +11,7 @@ import ctypes as C
 
 import torch
 
-from . import _decode, _lib
+from . import _decode, _lib, _status
 from ._lib import FA_BF16, FA_E4M3, FA_F16, FA_F32, FA_NVFP4
 
 _TORCH_TO_FA = {torch.float16: FA_F16, torch.bfloat16: FA_BF16, torch.float32: FA_F32}
@@ -122,17 +122,15 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
               and l_pool.shape[0] * page_size * DQK * 2 <= _expand_budget_bytes())
     tc_shape = tc_geometry and (fmt == FA_BF16 or expand)
     if tc_shape:
-        # the tensor-core kernel stages at most 128 block-table entries per CTA: bound the key ranges
-        import os
-        single = engine_hint == 3 or os.environ.get("FA_B200_MLA_PAIR", "1")[:1] == "0"
-        cap = lib.fa_mla_tc_max_range(page_size) if single else lib.fa_mla_pair_max_range(page_size)
+        # the tensor-core kernel stages a bounded number of block-table entries per CTA pair: bound the ranges
+        cap = lib.fa_mla_pair_max_range(page_size)
         if chunk_hint:
             chunk_hint = min(int(chunk_hint), cap)
         else:
             # A key range costs ~15 us of pipeline fill and drain in these kernels (measured), so sequences
-            # stay whole while there is one (sequence, 128-row tile) unit per CTA pair / CTA; fewer units
+            # stay whole while there is one (sequence, 128-row tile) unit per CTA pair; fewer units
             # are cut into about two ranges per slot, never shorter than 2048 keys.
-            slots = max(1, _decode.sm_count(dev) // (1 if single else 2))
+            slots = max(1, _decode.sm_count(dev) // 2)
             units = B * ((H_q * N_q + 127) // 128)
             total = sum(lens) if lens is not None else n_max * B
             if units >= slots:
@@ -174,4 +172,5 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
     a.engine_hint = int(engine_hint)
     with torch.cuda.device(dev):
         _lib.check(lib.fa_mla_decode_fwd(C.byref(a)), "fa_mla_decode_fwd")
+    _status.after_call(dev)
     return (out, lse) if return_lse else out

@@ -50,6 +50,23 @@ def kv_range_shards(n_k: int, page_size: int, world: int) -> List[Tuple[int, int
     return out
 
 
+_exchange: dict = {}
+
+
+def _exchange_buffers(device, world: int, n_floats: int):
+    import torch
+    stream = torch.cuda.current_stream(device).cuda_stream if device.type == "cuda" else 0
+    key = (str(device), stream, world, n_floats)
+    hit = _exchange.get(key)
+    if hit is None:
+        hit = (torch.empty(n_floats, dtype=torch.float32, device=device),
+               torch.empty(world, n_floats, dtype=torch.float32, device=device))
+        if len(_exchange) >= 16:
+            _exchange.pop(next(iter(_exchange)))
+        _exchange[key] = hit
+    return hit
+
+
 def kv_range_decode(attention_fn: Callable, q, args_before_n_k: Sequence, args_after_n_k: Sequence = (), *,
                     local_n_k, key_begin: int, causal: bool = False, q_offset: int = 0, value_dim: Optional[int] = None,
                     group=None, out_dtype=None, return_lse: bool = False, merge_fn: Optional[Callable] = None, **kw):
@@ -71,8 +88,9 @@ def kv_range_decode(attention_fn: Callable, q, args_before_n_k: Sequence, args_a
     D = int(value_dim) if value_dim is not None else q.shape[-1]
     rows = B * H_q * N_q
     # one flat buffer per rank, [rows * D outputs | rows lse], written by the kernel itself, so that a
-    # single all-gather moves both
-    send = torch.empty(rows * (D + 1), dtype=torch.float32, device=q.device)
+    # single all-gather moves both; send and receive buffers are kept per (device, stream, shape), so a
+    # decode loop allocates nothing here and a captured CUDA graph keeps valid addresses
+    send, recv = _exchange_buffers(q.device, world, rows * (D + 1))
     o_loc = send[: rows * D].view(B, H_q, N_q, D)
     lse_loc = send[rows * D:].view(B, H_q, N_q)
     if isinstance(local_n_k, int) and local_n_k == 0:
@@ -81,7 +99,6 @@ def kv_range_decode(attention_fn: Callable, q, args_before_n_k: Sequence, args_a
     else:
         attention_fn(q, *args_before_n_k, local_n_k, *args_after_n_k, causal=causal, q_offset=q_offset - key_begin,
                      out_dtype=torch.float32, out=o_loc, lse_out=lse_loc, **kw)
-    recv = torch.empty(world, rows * (D + 1), dtype=torch.float32, device=q.device)
     dist.all_gather_into_tensor(recv.view(-1), send, group=group)
     o_parts = recv[:, : rows * D].unflatten(1, (B, H_q, N_q, D))
     lse_parts = recv[:, rows * D:].unflatten(1, (B, H_q, N_q))

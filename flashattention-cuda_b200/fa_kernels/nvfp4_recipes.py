@@ -68,3 +68,41 @@ def fp8_attn_rmse(q, k, v, *, causal: bool = False) -> float:
     kq = dequantize_fp8_e4m3(*quantize_fp8_e4m3(k)).to(k.dtype)
     vq = dequantize_fp8_e4m3(*quantize_fp8_e4m3(v)).to(v.dtype)
     return _rmse(_gqa_attention(q, kq, vq, causal), _gqa_attention(q, k, v, causal))
+
+
+def fp4_score_collapse_rmse(q, k, v, *, causal: bool = False) -> dict:
+    """FP4 for the softmax weights as well as for the KV cache (reference nvfp4_recipes.py:105-142):
+    output RMSE against exact attention of (a) "fp4_kv_only": K quantised per channel, V per token, exact
+    weights; (b) "fp4_kv_and_p": the same with the weights P quantised per query row and renormalised.
+
+    This is the one function of the study that needs the weights themselves, which no attention kernel
+    materialises: as in the reference, the [N_q, N_k] score matrix is built with plain fp32 matrix
+    products (torch, on the GPU); every quantisation step runs through this library's kernels."""
+    import torch
+
+    G = q.shape[1] // k.shape[1]
+
+    def expand(x):
+        return x.repeat_interleave(G, dim=1).float() if G > 1 else x.float()
+
+    qf = q.float()
+    scale = 1.0 / (q.shape[-1] ** 0.5)
+    mask = None
+    if causal:
+        mask = torch.triu(torch.ones(q.shape[-2], k.shape[-2], device=q.device, dtype=torch.bool), diagonal=1)
+
+    def weights(keys):
+        s = torch.matmul(qf, keys.transpose(-1, -2)) * scale
+        if mask is not None:
+            s = s.masked_fill(mask, float("-inf"))
+        return torch.softmax(s, dim=-1)
+
+    ve = expand(v)
+    out_ref = torch.matmul(weights(expand(k)), ve)
+    vq = expand(fake_quant_nvfp4(v, "token"))
+    p_kv = weights(expand(fake_quant_nvfp4(k, "channel")))
+    out_kv = torch.matmul(p_kv, vq)
+    p_q = fake_quant_nvfp4(p_kv, "token")
+    p_q = p_q / p_q.sum(dim=-1, keepdim=True).clamp_min(1e-12)
+    out_pq = torch.matmul(p_q, vq)
+    return {"fp4_kv_only": _rmse(out_kv, out_ref), "fp4_kv_and_p": _rmse(out_pq, out_ref)}

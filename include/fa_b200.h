@@ -48,6 +48,26 @@ enum fa_dtype {
 
 FA_API const char* fa_last_error(void);
 FA_API int fa_version(void);
+
+/* Device status word.  Kernels never follow a bad block-table entry and never wait without a bound; what
+ * they met instead is recorded in one int32 in device memory that the host reads after the step: word 0
+ * of the `counters` buffer of the decode / MLA entry points, `fa_dense_args.status` for dense attention.
+ * The word is sticky: kernels only OR / compare-and-swap into it and the caller clears it after reading.
+ *   bit 16 (FA_STATUS_BAD_BLOCK_TABLE): a block-table entry outside [0, num_blocks) was met; the page was
+ *           treated as masked (decode) or read from block 0 (MLA tensor-core kernel), the output is wrong
+ *   bits 0..15: code of the first pipeline wait that gave up after its cycle bound (21..26 dense attention,
+ *           41..49 MLA CTA-pair kernel); the kernel ended early and the output is invalid
+ * A non-zero word after a launch also means the arrival counters behind it may not be zero again: zero
+ * the whole counters buffer before the next launch.  (The reference has no counterpart: its kernels read
+ * whatever the table holds, kernels/v8_gqa_ss/gqa_ss_attention.cu:124-136.) */
+#define FA_STATUS_BAD_BLOCK_TABLE 0x10000
+/* Text for a status word (static storage, valid until the next call on the same thread). */
+FA_API const char* fa_status_text(int status_word);
+/* Self-test of the bounded waits (no counterpart in the reference, whose kernels have no waits): one warp
+ * waits on an mbarrier that nothing arrives on, gives up after `max_cycles` SM clock cycles, records `code`
+ * in `*status` (device int32, as above) and sets `*gave_up` (device int32, optional) to 1.  Lets a host
+ * check its handling of a timed-out kernel without disturbing a real pipeline. */
+FA_API int fa_selftest_bounded_wait(int32_t* status, long long max_cycles, int code, int32_t* gave_up, void* stream);
 /* Number of SMs of the current device (cached per device). */
 FA_API int fa_device_sm_count(int* sm_count);
 
@@ -130,9 +150,9 @@ typedef struct fa_decode_args {
   int out_dtype;
   float* lse;
   /* scratch: partial results of split sequences (fa_decode_workspace_bytes; contents need no
-   * initialisation) and arrival counters (fa_decode_counters_len int32 words, zero before the first
-   * call; the kernel leaves them zero again, the last word collects error flags).  Neither may be
-   * shared by decode calls that overlap in time. */
+   * initialisation) and fa_decode_counters_len int32 words, zero before the first call: word 0 is the
+   * device status word (see above), the others are arrival counters, which the kernel leaves zero
+   * again.  Neither may be shared by decode calls that overlap in time. */
   void* workspace;
   size_t workspace_bytes;
   int32_t* counters;
@@ -184,16 +204,22 @@ FA_API int fa_paged_decode_host(const fa_decode_host_args* args);
  * The `workspace`, `workspace_bytes`, `counters` and `counters_len` fields of `args` are ignored: the
  * scratch is a fixed array of FA_DECODE_STATIC_SCRATCH_BYTES inside the library's device image.  The
  * call allocates nothing (no cudaMalloc / cudaFree, no library routine that allocates).
- *   - Limits: at most 16384 (sequence, KV head, 16-row tile) units per call, and the partial results of
- *     split sequences (fa_decode_workspace_bytes) must fit in the remaining bytes; beyond either limit
- *     the call returns FA_ERR_WORKSPACE and launches nothing.
+ *   - Limits: at most 16384 (sequence, KV head, 16-row tile) units per call, i.e. B * H_kv *
+ *     ceil((H_q / H_kv) * N_q / 16) <= 16384, and the partial results of split sequences
+ *     (fa_decode_workspace_bytes) must fit in the remaining FA_DECODE_STATIC_SCRATCH_BYTES - 65792 bytes;
+ *     beyond either limit the call returns FA_ERR_WORKSPACE and launches nothing.  Every argument is
+ *     checked before the call touches the array.
  *   - The first call on each device looks up the array's device address; make that first call outside
  *     any stream capture.
  *   - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
  *     streams, different threads) race on it and give wrong results.  Serialise them, or use
- *     fa_paged_decode_fwd with one scratch buffer per concurrent call. */
+ *     fa_paged_decode_fwd with one scratch buffer per concurrent call.
+ *   - The device status word of these calls lives in the array too and is kept until it is read:
+ *     fa_paged_decode_static_status copies it to `status_host`, optionally clears it, and waits for
+ *     `stream` (the one call of this header that synchronises). */
 #define FA_DECODE_STATIC_SCRATCH_BYTES (8u << 20)
 FA_API int fa_paged_decode_fwd_static(const fa_decode_args* args);
+FA_API int fa_paged_decode_static_status(int32_t* status_host, int clear, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Merge of normalised partial outputs over disjoint key ranges (the algebra of the reference merge
@@ -245,9 +271,9 @@ FA_API int fa_dense_fwd(const fa_dense_args* args);
  *             per-token scales of an E4M3 latent (multiply l_scale)
  *   (DQK, DV) in {(576,512), (160,128), (96,64)} as in kernels/v11_mla/mla_attention.cu:383-397.
  * Plan, workspace and counters as for fa_paged_decode_fwd, with H_kv = 1 and 32-row tiles: call
- * fa_decode_plan(..., H_kv = 1, rows = 16 * ceil(H_q * N_q / 32), chunk_hint <= fa_mla_tc_max_range(page_size)
+ * fa_decode_plan(..., H_kv = 1, rows = 16 * ceil(H_q * N_q / 32), chunk_hint <= fa_mla_pair_max_range(page_size)
  * to allow the tcgen05 kernel), workspace bytes = fa_mla_workspace_bytes(n_slots, H_q, N_q, DV), counters =
- * fa_mla_counters_len(B, H_q, N_q).
+ * fa_mla_counters_len(B, H_q, N_q) (word 0 is the device status word).
  * ---------------------------------------------------------------------------------------------- */
 typedef struct fa_mla_args {
   const void* q;
@@ -278,14 +304,14 @@ typedef struct fa_mla_args {
   int32_t* counters;
   size_t counters_len;
   void* stream;
-  int engine_hint;   /* 0 = choose (tcgen05 on a CTA pair where it applies); 2 = force the mma.sync kernel;
-                        3 = the single-CTA tcgen05 kernel instead of the pair.  The tcgen05 kernels need a
-                        bf16 (576, 512) latent, page_size a power of two >= 64 and key ranges <=
-                        fa_mla_tc_max_range */
+  int engine_hint;   /* 0 = choose (tcgen05 on a CTA pair where it applies); 2 = force the mma.sync kernel.
+                        The tcgen05 kernel needs a bf16 (576, 512) latent, page_size a power of two >= 64
+                        and key ranges <= fa_mla_pair_max_range; everything else (FP8 / NVFP4 latents read
+                        in place, the (160, 128) and (96, 64) geometries, other page sizes) runs on the
+                        mma.sync kernel */
 } fa_mla_args;
 FA_API size_t fa_mla_counters_len(int B, int H_q, int N_q);
 FA_API size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV);
-FA_API int fa_mla_tc_max_range(int page_size);     /* longest key range of the single-CTA tcgen05 kernel */
 FA_API int fa_mla_pair_max_range(int page_size);   /* longest key range of the CTA-pair kernel */
 FA_API int fa_mla_decode_fwd(const fa_mla_args* args);
 /* Expand the tokens of the planned key ranges of a quantised latent pool into a bf16 pool of the same

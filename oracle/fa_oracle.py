@@ -336,3 +336,38 @@ def fp8_attn_rmse(q, k, v, *, causal=False):
     out_q = gqa_attention_ref(q, kq, vq, causal=causal)
     out_ref = gqa_attention_ref(q, k, v, causal=causal)
     return float(np.sqrt(np.mean((out_q - out_ref) ** 2)))
+
+
+def fp4_score_collapse_rmse(q, k, v, *, causal=False):
+    """fa_kernels/nvfp4_recipes.py:105-142: output RMSE against exact attention of (a) K quantised per
+    channel and V per token with exact softmax weights, (b) the same with the softmax weights themselves
+    quantised per query row (token granularity) and renormalised.  fp32 arithmetic as in the reference."""
+    q = np.asarray(q, dtype=np.float32)
+    k = np.asarray(k, dtype=np.float32)
+    v = np.asarray(v, dtype=np.float32)
+    G = q.shape[1] // k.shape[1]
+    expand = (lambda x: np.repeat(x, G, axis=1)) if G > 1 else (lambda x: x)
+    scale = np.float32(1.0 / np.sqrt(q.shape[-1]))
+    n_q, n_k = q.shape[2], k.shape[2]
+    mask = np.triu(np.ones((n_q, n_k), dtype=bool), k=1) if causal else None
+
+    def softmax_rows(scores):
+        if mask is not None:
+            scores = np.where(mask, -np.inf, scores)
+        e = np.exp(scores - scores.max(axis=-1, keepdims=True))
+        return (e / e.sum(axis=-1, keepdims=True)).astype(np.float32)
+
+    ke, ve = expand(k), expand(v)
+    out_ref = np.matmul(softmax_rows(np.matmul(q, ke.transpose(0, 1, 3, 2)) * scale), ve)
+    kq = expand(fake_quant_nvfp4(k, "channel"))
+    vq = expand(fake_quant_nvfp4(v, "token"))
+    p_kv = softmax_rows(np.matmul(q, kq.transpose(0, 1, 3, 2)) * scale)
+    out_kv = np.matmul(p_kv, vq)
+    p_q = fake_quant_nvfp4(p_kv, "token")
+    p_q = p_q / np.maximum(p_q.sum(axis=-1, keepdims=True), np.float32(1e-12))
+    out_pq = np.matmul(p_q, vq)
+
+    def rmse(a, b):
+        return float(np.sqrt(np.mean((a.astype(np.float64) - b.astype(np.float64)) ** 2)))
+
+    return {"fp4_kv_only": rmse(out_kv, out_ref), "fp4_kv_and_p": rmse(out_pq, out_ref)}

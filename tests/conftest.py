@@ -45,3 +45,18 @@ def golden():
     def load(name):
         return np.load(os.path.join(GOLDEN_DIR, name))
     return load
+
+
+@pytest.fixture(autouse=True)
+def _device_status_is_clean(request):
+    """After every GPU test: no kernel of the test left an error in a device status word (a masked
+    block-table entry, a pipeline wait that gave up).  Tests that provoke a flag clear it themselves."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from fa_kernels import _status
+    if _status._buffers:
+        assert _status.read_status() == 0, "a kernel of this test recorded a device status: " + hex(_status.read_status())

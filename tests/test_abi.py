@@ -130,3 +130,78 @@ def test_sweep_takes_the_reference_harness_flags():
     assert a.seq == [8192] and a.dim == [64, 128] and a.page_size == 256 and a.causal
     b = parse("--backend v12_mla_tc --mla-engine nvfp4 --kv-lens 8192 1048576 --h-kv 1 8 --max-ws-gb 8 --batch 2".split())
     assert b.mla_engine == "nvfp4" and b.seq == [8192, 1048576] and b.h_kvs == [1, 8] and b.max_ws_gb == 8.0 and b.batch == 2
+
+
+def test_planner_ranges_never_exceed_what_the_kernels_stage():
+    """A range of n keys may touch n / page + 2 block-table entries; the decode kernel stages at most 2048
+    of them, the MLA kernels 2048 (fused) and 512 (CTA pair, through the chunk hint the host passes).
+    Lengths around the multiples of the longest range are where an off-by-one would show."""
+    from fa_kernels import _lib
+    lib = _lib.load()
+    for page in (16, 64, 128, 256):
+        longest = 2046 * page
+        for ns in (1, 2, 3):
+            for delta in (-130, -64, -1, 0, 1, 63, 64, 65, 200):
+                n = ns * longest + delta
+                if n <= 0:
+                    continue
+                for B in (1, 4, 64):
+                    _, mr = _plan(lib, [n] * B, 0, 8, 4, page, 148)
+                    assert mr // page + 2 <= 2048, (page, n, B, mr)
+                    _, mr = _plan(lib, [n] * B, 0, 1, 64, page, 148)          # the fused MLA kernel's plan
+                    assert mr // page + 2 <= 2048, (page, n, B, mr)
+        if page >= 64:
+            cap = lib.fa_mla_pair_max_range(page)
+            assert cap % 128 == 0 and cap // page + 2 <= 512
+            for n in (cap - 1, cap, cap + 1, 2 * cap - 64, 2 * cap + 64, 5 * cap + 1):
+                _, mr = _plan(lib, [n, 4096], 0, 1, 64, page, 148, hint=cap)
+                assert mr <= cap and mr // page + 2 <= 512, (page, n, mr, cap)
+    # the contexts that used to be rejected: 64 sequences of 131008 / 262000 keys at page 64
+    for n in (131008, 262000, 130945):
+        _, mr = _plan(lib, [n] * 64, 0, 8, 4, 64, 148)
+        assert mr // 64 + 2 <= 2048
+
+
+def test_status_words_have_text():
+    from fa_kernels import _lib
+    lib = _lib.load()
+    assert lib.fa_status_text(0) == b"ok"
+    assert b"block-table entry" in lib.fa_status_text(0x10000)
+    t = lib.fa_status_text(0x10000 | 47)
+    assert b"MLA pair kernel" in t and b"block-table entry" in t
+    assert b"dense attention" in lib.fa_status_text(22)
+    assert b"timed out" in lib.fa_status_text(999)
+
+
+def test_roofline_work_counts_match_the_reference_formulas():
+    """fa_bench/roofline.py against the numbers the reference's formulas give for the five benchmark
+    configurations (roofline/model.py:107-116, 137-142, 197-199) and its three-way bound."""
+    import importlib.util
+    path = os.path.join(REPO_ROOT, "flashattention-cuda_b200", "fa_bench", "roofline.py")
+    spec = importlib.util.spec_from_file_location("fa_roofline", path)
+    R = importlib.util.module_from_spec(spec)
+    import sys
+    sys.modules["fa_roofline"] = R
+    spec.loader.exec_module(R)
+    w = R.dense_attention(4, 32, 4096, 4096, 128, causal=True)
+    assert w.flops == 2 * 4 * 32 * 128 * 4096 * 4097 and abs(w.flops - 5.499e11) < 1e8
+    assert R.dense_attention_full_flops(4, 32, 4096, 4096, 128) == 4 * 4 * 32 * 4096 * 4096 * 128
+    assert w.total_bytes == 4 * 4 * 32 * 4096 * 128 * 2
+    d = R.paged_decode(1000, H_q=32, H_kv=8, d=128)
+    assert d.kv_bytes == 4096 * 1000 and d.flops == 4 * 32 * 128 * 1000 and abs(d.flops / d.kv_bytes - 4.0) < 1e-9
+    f8 = R.paged_decode(4 * 1048576, H_q=32, H_kv=8, d=128, kv_format="e4m3", per_token_scales=True, B=4)
+    assert abs(f8.kv_bytes - 8.858e9) < 1e6
+    f4 = R.paged_decode(4 * 1048576, H_q=32, H_kv=8, d=128, kv_format="nvfp4", B=4)
+    assert abs(f4.kv_bytes - 4.832e9) < 1e6
+    m = R.mla_decode(1000, h_q=128)
+    assert m.flops == 278528 * 1000 and m.kv_bytes == 1152 * 1000
+    assert R.mla_decode(1000, h_q=128, latent_format="e4m3", per_token_scales=True).kv_bytes == 580 * 1000
+    nominal = R.nominal_peaks()
+    lb = R.lower_bound(w, nominal)
+    assert lb["limiter"] == "mma" and abs(lb["seconds"] - w.flops / 2.25e15) < 1e-12 and abs(lb["ridge"] - 281.25) < 1e-6
+    assert R.lower_bound(d, nominal)["limiter"] == "hbm"
+    # MLA with a bf16 latent sits just under the ridge (hbm), with an FP8 latent above it (mma)
+    assert R.lower_bound(R.mla_decode(128 * 18432, h_q=128, B=128), nominal)["limiter"] == "hbm"
+    assert R.lower_bound(R.mla_decode(128 * 18432, h_q=128, latent_format="e4m3", per_token_scales=True, B=128), nominal)["limiter"] == "mma"
+    a = R.achieved(d, 1e-6, nominal)
+    assert a["bound"] == "hbm" and abs(a["achieved"] - 4096 * 1000 / 1e-6 / 1e9) < 1e-6 and abs(a["frac"] - a["achieved"] / 8000.0) < 1e-12

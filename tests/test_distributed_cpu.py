@@ -92,3 +92,52 @@ def test_kv_range_decode_protocol_on_gloo(world, causal):
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, port, causal, ret), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def _absent_rank_worker(rank, world, port, ret):
+    for p in (PKG_DIR, REPO_ROOT):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from fa_kernels.distributed import kv_range_decode, kv_range_shards
+    if rank == 1:
+        # this rank joined the group but never reaches the step's all-gather (a stalled worker)
+        ret[rank] = "absent"
+        time.sleep(10.0)
+        return
+    g = torch.Generator().manual_seed(7)
+    B, H_q, H_kv, N_q, d, page, n_k = 1, 2, 1, 1, 16, 16, 64
+    q = torch.randn(B, H_q, N_q, d, generator=g)
+    k = torch.randn(B, H_kv, n_k, d, generator=g)
+    v = torch.randn(B, H_kv, n_k, d, generator=g)
+    kb, ke = kv_range_shards(n_k, page, world)[rank]
+    t0 = time.time()
+    try:
+        kv_range_decode(_oracle_attention, q, (k[:, :, kb:ke].contiguous(), v[:, :, kb:ke].contiguous()),
+                        local_n_k=ke - kb, key_begin=kb, merge_fn=_oracle_merge)
+        ret[rank] = "returned"
+    except Exception as exc:                       # the collective's timeout surfaces as a Python exception
+        ret[rank] = f"raised {type(exc).__name__} after {time.time() - t0:.1f} s"
+
+
+def test_a_rank_that_never_joins_the_all_gather_becomes_an_exception():
+    """Failure detection on the host: with a process-group timeout, the rank that does reach the all-gather
+    of kv_range_decode gets an exception instead of waiting for ever (CPU ranks, gloo)."""
+    port = 31500 + os.getpid() % 2000
+    ret = mp.Manager().dict()
+    ctx = mp.spawn(_absent_rank_worker, args=(2, port, ret), nprocs=2, join=False)
+    deadline = 60.0
+    import time
+    t0 = time.time()
+    while time.time() - t0 < deadline and not str(ret.get(0, "")).startswith(("raised", "returned")):
+        time.sleep(0.2)
+    for p in ctx.processes:
+        p.join(timeout=15)
+        if p.is_alive():
+            p.terminate()
+    assert ret.get(1) == "absent"
+    assert str(ret.get(0, "")).startswith("raised"), dict(ret)

@@ -178,6 +178,30 @@ def test_recipe_rmse_close_to_reference_numbers():
     assert abs(got - want) <= 0.05 * want + 2e-4
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_score_collapse_study_matches_reference_fixture_and_oracle(causal, golden):
+    """fp4_score_collapse_rmse (reference nvfp4_recipes.py:105-142): on the reference's own fixture the two
+    figures agree with the numbers the reference computed, and on a larger seeded case (outlier channel and
+    outlier token) with the oracle, both inside the 5 % band of the other recipe metrics."""
+    from fa_kernels.nvfp4_recipes import fp4_score_collapse_rmse
+    if not causal:
+        g = golden("recipes.npz")
+        got = fp4_score_collapse_rmse(*(torch.from_numpy(g[x]).cuda() for x in ("q", "k", "v")))
+        for key, name in (("fp4_kv_only", "collapse_kv_only"), ("fp4_kv_and_p", "collapse_kv_and_p")):
+            assert abs(got[key] - float(g[name])) <= 0.05 * float(g[name]), (key, got, float(g[name]))
+    gen = torch.Generator().manual_seed(28)
+    n = 96
+    q = torch.randn(1, 4, n, 64, generator=gen)
+    k = torch.randn(1, 2, n, 64, generator=gen)
+    v = torch.randn(1, 2, n, 64, generator=gen)
+    k[..., 5] *= 10.0
+    v[:, :, 7, :] *= 10.0
+    got = fp4_score_collapse_rmse(q.cuda(), k.cuda(), v.cuda(), causal=causal)
+    want = O.fp4_score_collapse_rmse(q.numpy(), k.numpy(), v.numpy(), causal=causal)
+    for key in ("fp4_kv_only", "fp4_kv_and_p"):
+        assert abs(got[key] - want[key]) <= 0.05 * want[key] + 2e-4, (key, got, want)
+
+
 @pytest.mark.parametrize("fmt", ["f16", "e4m3", "nvfp4"])
 def test_append_token_by_token_equals_offline_build(fmt):
     """Appending tokens step by step (varied step sizes, per-sequence positions) must leave the pools
@@ -213,6 +237,21 @@ def test_append_token_by_token_equals_offline_build(fmt):
         np.testing.assert_array_equal(written, _np(P.paged_gather(ref_scales.unsqueeze(-1), bt, page, N)))
     if fmt == "nvfp4":
         np.testing.assert_array_equal(_np(extra["micro_pool"]), _np(ref_micro))
+    # and directly against the oracle: quantise the whole tensor on the CPU, page it with the same table
+    perm = _np(bt).reshape(-1)
+    xn = k.numpy()
+    if fmt == "f16":
+        want = O.paged_scatter(xn.astype(np.float16), page, perm)
+        np.testing.assert_array_equal(_np(pool).view(np.uint16), want.view(np.uint16))
+    elif fmt == "e4m3":
+        codes, scales = O.quantize_fp8_e4m3_per_token(xn)
+        np.testing.assert_array_equal(_np(pool), O.paged_scatter(codes, page, perm))
+        np.testing.assert_array_equal(_np(extra["scale_pool"]), O.paged_scatter(scales[..., None], page, perm)[..., 0])
+    else:
+        packed, micro, scale = O.quantize_nvfp4(xn)
+        assert np.float32(scale) == np.float32(extra["tensor_scale"])
+        np.testing.assert_array_equal(_np(pool), O.paged_scatter(packed, page, perm))
+        np.testing.assert_array_equal(_np(extra["micro_pool"]), O.paged_scatter(micro, page, perm))
 
 
 @pytest.mark.gpu

@@ -143,6 +143,9 @@ def test_nvfp4_recipes(golden):
     np.testing.assert_allclose(O.attn_rmse(q, k, v, k_gran="channel", v_gran="token"),
                                float(g["rmse_channel_token"]), rtol=1e-4)
     np.testing.assert_allclose(O.fp8_attn_rmse(q, k, v), float(g["rmse_fp8"]), rtol=1e-4)
+    col = O.fp4_score_collapse_rmse(q, k, v)
+    np.testing.assert_allclose(col["fp4_kv_only"], float(g["collapse_kv_only"]), rtol=1e-4)
+    np.testing.assert_allclose(col["fp4_kv_and_p"], float(g["collapse_kv_and_p"]), rtol=1e-3)
 
 
 def test_config1_cpu_plumbing(golden):

@@ -20,9 +20,8 @@ SHAPES = [(1, 4, 128, 64), (2, 8, 512, 64), (1, 8, 512, 128), (1, 2, 2048, 64), 
 
 
 def _status_ok():
-    from fa_kernels._dense import status_word
-    torch.cuda.synchronize()
-    assert int(status_word(torch.device("cuda", torch.cuda.current_device())).item()) == 0, "a pipeline wait timed out"
+    from fa_kernels import check_status
+    check_status()          # raises, naming the wait, if a bounded pipeline wait of the kernel gave up
 
 
 @pytest.mark.parametrize("B,H,N,d", SHAPES)
@@ -60,8 +59,17 @@ def test_rectangular_and_bf16(N_q, N_k, causal, dtype):
     out = attention(q_t.cuda(), k_t.cuda(), v_t.cuda(), causal=causal, out_dtype=dtype)
     _status_ok()
     assert out.dtype == dtype
-    tol = dict(atol=2e-3, rtol=1e-2) if dtype == torch.float16 else dict(atol=8e-3, rtol=2e-2)
-    assert_close(out, O.attention_ref(q, k, v, causal=causal), what="rect", **tol)
+    ref = O.attention_ref(q, k, v, causal=causal)
+    if dtype == torch.float16:
+        assert_close(out, ref, what="rect")
+    else:
+        # The 2e-3 / 1e-2 band is about the arithmetic, so it is held on the fp32 output of the bf16 inputs;
+        # a bf16 output adds its own rounding (half an ulp = 2^-9 relative, up to 8e-3 absolute at |o| ~ 2),
+        # which is checked as such: the bf16 output is the fp32 output rounded once.
+        out32 = attention(q_t.cuda(), k_t.cuda(), v_t.cuda(), causal=causal, out_dtype=torch.float32)
+        _status_ok()
+        assert_close(out32, ref, what="rect bf16 inputs, fp32 output")
+        assert torch.equal(out, out32.to(torch.bfloat16))
 
 
 def test_long_sequence_rescale_stability():
