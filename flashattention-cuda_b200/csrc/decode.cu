@@ -800,11 +800,20 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     slot += ns;
   }
   };
-  // Estimated length of the launch: every (range, head, row tile) CTA costs its keys plus the start-up,
-  // CTAs take the slots in launch order (longest range first), all at the same rate.  The H_kv x row-tile
+  // Estimated length of the launch, in units of the time one CTA needs for one key when every slot is busy.
+  // A fluid model fitted to measurements on B200 (fp16 KV, 8 KV heads, 8 / 16 / 32 sequences of 1024-8192 keys
+  // cut into ranges of 256 ... 8192 keys: 30 launches of 41 ... 190 us, rms error 2 %; FP8 KV, 4 sequences of
+  // 131072 / 524288 keys, ranges of 2048 ... 131072 keys: 17 launches, rms error 6 %): CTAs take the slots in
+  // launch order (longest range first); a CTA first spends a start-up (4 us for the fp16 kernel with two
+  // CTAs per SM, 2 us for the kernels with three: metadata, block table, first tiles in flight), then streams
+  // its keys; all streaming CTAs progress at the same rate, which falls linearly from 1.4 with one CTA per SM
+  // (a lone CTA is latency bound) to 1 with every slot streaming (the HBM or issue bound).  The H_kv x row-tile
   // CTAs of a range are equal and adjacent in launch order, so they are scheduled as one job on
   // slots / (H_kv x row tiles) groups of slots, which keeps this pass at a few microseconds.
-  auto estimate = [&](std::vector<fa_decode_item>& v) {
+  const double kCtasPerSm = num_sms > 0 ? 3.0 : 2.0;
+  const double kStartUp = num_sms > 0 ? 90.0 : 160.0;
+  constexpr double kSoloRate = 1.4;
+  auto estimate = [&](std::vector<fa_decode_item>& v) -> int64_t {
     std::stable_sort(v.begin(), v.end(), [](const fa_decode_item& a, const fa_decode_item& b2) {
       return (a.k_end - a.k_begin) > (b2.k_end - b2.k_begin);
     });
@@ -812,19 +821,48 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     const int64_t groups = slots / per_item;
     if (groups <= 1) {
       int64_t sum = 0;
-      for (const fa_decode_item& it : v) sum += (it.k_end - it.k_begin) + 500;
+      for (const fa_decode_item& it : v) sum += (it.k_end - it.k_begin) + (int64_t)kStartUp;
       return sum * per_item / std::max<int64_t>(slots, 1);
     }
-    std::vector<int64_t> heap((size_t)groups, 0);
-    auto later = [](int64_t x, int64_t y) { return x > y; };
-    int64_t makespan = 0;
-    for (const fa_decode_item& it : v) {
-      std::pop_heap(heap.begin(), heap.end(), later);
-      heap.back() += (it.k_end - it.k_begin) + 500;
-      makespan = std::max(makespan, heap.back());
-      std::push_heap(heap.begin(), heap.end(), later);
+    // min-heaps: CTAs still starting up (by the time they begin to stream), streaming CTAs (by the value of
+    // the common progress counter at which they finish)
+    std::vector<std::pair<double, int>> starting;
+    std::vector<double> streaming;
+    auto later_s = [](const std::pair<double, int>& x, const std::pair<double, int>& y) { return x.first > y.first; };
+    auto later_d = [](double x, double y) { return x > y; };
+    size_t next = 0;
+    double t = 0.0, progress = 0.0;
+    auto dispatch = [&]() {
+      while (next < v.size() && (int64_t)(starting.size() + streaming.size()) < groups) {
+        starting.emplace_back(t + kStartUp, v[next].k_end - v[next].k_begin);
+        std::push_heap(starting.begin(), starting.end(), later_s);
+        ++next;
+      }
+    };
+    dispatch();
+    while (!starting.empty() || !streaming.empty()) {
+      const double per_sm = kCtasPerSm * (double)streaming.size() / (double)groups;      // streaming CTAs per SM
+      const double rate = streaming.empty() ? 0.0
+                          : std::max(1.0, std::min(kSoloRate, kSoloRate - (kSoloRate - 1.0) * (per_sm - 1.0) / (kCtasPerSm - 1.0)));
+      const double t_start = starting.empty() ? 1e300 : starting.front().first;
+      const double t_finish = streaming.empty() ? 1e300 : t + (streaming.front() - progress) / rate;
+      if (t_start <= t_finish) {
+        progress += rate * (t_start - t);
+        t = t_start;
+        const int keys = starting.front().second;
+        std::pop_heap(starting.begin(), starting.end(), later_s);
+        starting.pop_back();
+        streaming.push_back(progress + keys);
+        std::push_heap(streaming.begin(), streaming.end(), later_d);
+      } else {
+        progress = streaming.front();
+        t = t_finish;
+        std::pop_heap(streaming.begin(), streaming.end(), later_d);
+        streaming.pop_back();
+        dispatch();
+      }
     }
-    return makespan;
+    return (int64_t)t;
   };
   std::vector<fa_decode_item> v;
   int max_range = 0;
@@ -832,12 +870,12 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
     build(false, 1, v, max_range);                       // as asked, or enough whole sequences for many waves
   } else {
     // few waves: whole sequences leave the last wave partly empty; two or three equal ranges per sequence,
-    // or shrinking ranges, fill it at the price of a start-up (~500 keys) per range.  Take the candidate
+    // or shrinking ranges, fill it at the price of a start-up per range.  Take the candidate
     // with the shortest estimated launch.
     build(false, 1, v, max_range);
     int64_t best = estimate(v);
     // no plan beats (all work + one start-up per unit) / slots: stop when whole sequences are within 6 % of it
-    const int64_t lower = (work + 500 * units) / std::max<int64_t>(slots, 1);
+    const int64_t lower = (work + (int64_t)kStartUp * units) / std::max<int64_t>(slots, 1);
     std::vector<fa_decode_item> alt;
     int alt_range = 0;
     // shrinking ranges only pay when there are fewer units than slots; with more they are not tried
@@ -851,6 +889,39 @@ extern "C" int fa_decode_plan(const int32_t* seq_lens_host, int n_k, int B, int 
         max_range = alt_range;
       }
     }
+    // Full waves of equal ranges: the shortest common range length whose CTAs still fit w waves of slots,
+    // every sequence cut into equal parts no longer than that.  A launch that is one (or two, three) full
+    // waves has no partly empty last wave, and for small jobs -- what one GPU of several sees of a sharded
+    // batch -- it beats the shrinking ranges (measured on 8 sequences of ~5000 keys, 8 KV heads: 41 us for
+    // one wave of 288 CTAs against 47 us for 488 CTAs of shrinking ranges).
+    const int64_t per_item = (int64_t)H_kv * row_tiles;
+    auto ctas_at = [&](int64_t len_cap) {
+      int64_t n = 0;
+      for (int b = 0; b < B; ++b) {
+        const int64_t len = seq_lens_host ? seq_lens_host[b] : n_k;
+        n += std::max<int64_t>((len + len_cap - 1) / len_cap, 1) * per_item;
+      }
+      return n;
+    };
+    const int64_t saved_chunk = chunk;
+    for (int waves = 1; waves <= 3 && best * 100 > lower * 106; ++waves) {
+      if (ctas_at(max_chunk) > waves * slots) continue;               // not even the longest ranges fit
+      int64_t lo = 1, hi = max_chunk / kTN;                            // in tiles: smallest cap that fits
+      while (lo < hi) {
+        const int64_t mid = (lo + hi) / 2;
+        if (ctas_at(mid * kTN) <= waves * slots) hi = mid; else lo = mid + 1;
+      }
+      chunk = lo * kTN;
+      if (chunk < 256) break;                                          // ranges this short are all start-up
+      build(false, 1, alt, alt_range);
+      const int64_t t = estimate(alt);
+      if (t < best) {
+        best = t;
+        v = alt;
+        max_range = alt_range;
+      }
+    }
+    chunk = saved_chunk;
   }
   std::stable_sort(v.begin(), v.end(), [](const fa_decode_item& a, const fa_decode_item& b2) {
     return (a.k_end - a.k_begin) > (b2.k_end - b2.k_begin);

@@ -518,47 +518,72 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // after a wait that gave up the ticket is still taken, so that the counters are zero again for the next
   // launch, but there is nothing valid to merge (the status word tells the host)
   if (*s_abort) return;
-  constexpr int kU = 8;
-  for (int idx = threadIdx.x; idx < rows_valid * (kPDV / 4); idx += kPThreads) {
-    const int row = idx / (kPDV / 4), d4 = idx - row * (kPDV / 4);
-    const int m = m0 + row;
-    const float* lse_base = p.part_lse + (int64_t)it.slot_base * p.M + m;
-    const float4* o_base = reinterpret_cast<const float4*>(p.part_o + ((int64_t)it.slot_base * p.M + m) * kPDV) + d4;
-    float m_run = -INFINITY, l = 0.f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s0 = 0; s0 < it.n_split; s0 += kU) {
-      float ls[kU];
-      float4 ov[kU];
+  // A thread owns (row, four output columns) quads; the partials of kU ranges of kI quads are fetched before
+  // any is used, so that a merge over n ranges of the 64 x 512 outputs of this CTA costs about
+  // (8192 / 256 / kI) * ceil(n / kU) L2 round trips instead of one per quad.
+  constexpr int kU = 4, kI = 4;
+  const int n_quads = rows_valid * (kPDV / 4);
+  for (int idx0 = threadIdx.x; idx0 < n_quads; idx0 += kPThreads * kI) {
+    const float* lse_base[kI];
+    const float4* o_base[kI];
+    float m_run[kI], l[kI];
+    float4 acc[kI];
+    bool live[kI];
 #pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const int sidx = min(s0 + u, it.n_split - 1);
-        ls[u] = __ldcg(lse_base + (int64_t)sidx * p.M);
-        ov[u] = __ldcg(o_base + (int64_t)sidx * p.M * (kPDV / 4));
-        if (s0 + u >= it.n_split) ls[u] = -INFINITY;
-      }
-      float mb = m_run;
-#pragma unroll
-      for (int u = 0; u < kU; ++u) mb = fmaxf(mb, ls[u]);
-      if (mb == -INFINITY) continue;
-      const float resc = __expf(m_run - mb);
-      acc.x *= resc, acc.y *= resc, acc.z *= resc, acc.w *= resc, l *= resc;
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        const float wgt = __expf(ls[u] - mb);
-        acc.x += wgt * ov[u].x, acc.y += wgt * ov[u].y, acc.z += wgt * ov[u].z, acc.w += wgt * ov[u].w;
-        l += wgt;
-      }
-      m_run = mb;
+    for (int q = 0; q < kI; ++q) {
+      const int idx = idx0 + q * kPThreads;
+      live[q] = idx < n_quads;
+      const int row = live[q] ? idx / (kPDV / 4) : 0, d4 = live[q] ? idx - row * (kPDV / 4) : 0;
+      const int m = m0 + row;
+      lse_base[q] = p.part_lse + (int64_t)it.slot_base * p.M + m;
+      o_base[q] = reinterpret_cast<const float4*>(p.part_o + ((int64_t)it.slot_base * p.M + m) * kPDV) + d4;
+      m_run[q] = -INFINITY, l[q] = 0.f, acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float inv = (l > 0.f) ? 1.f / l : 0.f;
-    const int h = m / p.N_q, iq = m - h * p.N_q;
-    const int64_t orow = ((int64_t)b * p.H_q + h) * p.N_q + iq;
-    const int64_t o0 = orow * kPDV + d4 * 4;
-    store_out_dyn(p.out, p.out_dtype, o0 + 0, acc.x * inv);
-    store_out_dyn(p.out, p.out_dtype, o0 + 1, acc.y * inv);
-    store_out_dyn(p.out, p.out_dtype, o0 + 2, acc.z * inv);
-    store_out_dyn(p.out, p.out_dtype, o0 + 3, acc.w * inv);
-    if (p.lse && d4 == 0) p.lse[orow] = (l > 0.f) ? m_run + __logf(l) : -INFINITY;
+    for (int s0 = 0; s0 < it.n_split; s0 += kU) {
+      float ls[kI][kU];
+      float4 ov[kI][kU];
+#pragma unroll
+      for (int q = 0; q < kI; ++q)
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int sidx = min(s0 + u, it.n_split - 1);
+          ls[q][u] = __ldcg(lse_base[q] + (int64_t)sidx * p.M);
+          ov[q][u] = __ldcg(o_base[q] + (int64_t)sidx * p.M * (kPDV / 4));
+          if (s0 + u >= it.n_split) ls[q][u] = -INFINITY;
+        }
+#pragma unroll
+      for (int q = 0; q < kI; ++q) {
+        float mb = m_run[q];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) mb = fmaxf(mb, ls[q][u]);
+        if (mb == -INFINITY) continue;
+        const float resc = __expf(m_run[q] - mb);
+        acc[q].x *= resc, acc[q].y *= resc, acc[q].z *= resc, acc[q].w *= resc, l[q] *= resc;
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const float wgt = __expf(ls[q][u] - mb);
+          acc[q].x += wgt * ov[q][u].x, acc[q].y += wgt * ov[q][u].y, acc[q].z += wgt * ov[q][u].z, acc[q].w += wgt * ov[q][u].w;
+          l[q] += wgt;
+        }
+        m_run[q] = mb;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kI; ++q) {
+      if (!live[q]) continue;
+      const int idx = idx0 + q * kPThreads;
+      const int row = idx / (kPDV / 4), d4 = idx - row * (kPDV / 4);
+      const int m = m0 + row;
+      const float inv = (l[q] > 0.f) ? 1.f / l[q] : 0.f;
+      const int h = m / p.N_q, iq = m - h * p.N_q;
+      const int64_t orow = ((int64_t)b * p.H_q + h) * p.N_q + iq;
+      const int64_t o0 = orow * kPDV + d4 * 4;
+      store_out_dyn(p.out, p.out_dtype, o0 + 0, acc[q].x * inv);
+      store_out_dyn(p.out, p.out_dtype, o0 + 1, acc[q].y * inv);
+      store_out_dyn(p.out, p.out_dtype, o0 + 2, acc[q].z * inv);
+      store_out_dyn(p.out, p.out_dtype, o0 + 3, acc[q].w * inv);
+      if (p.lse && d4 == 0) p.lse[orow] = (l[q] > 0.f) ? m_run[q] + __logf(l[q]) : -INFINITY;
+    }
   }
 }
 

@@ -127,17 +127,28 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
         if chunk_hint:
             chunk_hint = min(int(chunk_hint), cap)
         else:
-            # A key range costs ~15 us of pipeline fill and drain in these kernels (measured), so sequences
-            # stay whole while there is one (sequence, 128-row tile) unit per CTA pair; fewer units
-            # are cut into about two ranges per slot, never shorter than 2048 keys.
+            # A key range costs tens of microseconds of pipeline fill, drain and merge in this kernel (measured),
+            # so sequences stay whole while there is one (sequence, 128-row tile) unit per CTA pair.  With fewer
+            # units -- what one GPU of several sees of a sharded batch -- the sequences are cut into equal
+            # ranges under the shortest common cap that fills one wave of pairs, or two waves when more than
+            # half of the pairs would hold a whole sequence anyway (measured on 16 / 32 / 64 sequences of
+            # 4096-32768 keys: 139 / 232 / 397 us against 197 / 277 / 434 us for two ranges per pair).
             slots = max(1, _decode.sm_count(dev) // 2)
-            units = B * ((H_q * N_q + 127) // 128)
-            total = sum(lens) if lens is not None else n_max * B
+            tiles = (H_q * N_q + 127) // 128
+            units = B * tiles
             if units >= slots:
                 chunk_hint = cap
             else:
-                want = -(-total * ((H_q * N_q + 127) // 128) // (2 * slots))
-                chunk_hint = min(cap, max(2048, -(-want // 128) * 128))
+                seq = lens if lens is not None else (n_max,) * B
+                budget = slots if 2 * units <= slots else 2 * slots
+                lo, hi = 8, max(8, cap // 128)                   # cap in 128-key tiles; at least 1024 keys
+                while lo < hi:
+                    mid = (lo + hi) // 2
+                    if sum(max(1, -(-n // (mid * 128))) for n in seq) * tiles <= budget:
+                        hi = mid
+                    else:
+                        lo = mid + 1
+                chunk_hint = min(cap, lo * 128)
     items, n_items, n_slots, max_range, _ = _decode.plan(lens, n_max, B, 1, rows32, page_size, dev, int(chunk_hint))
     ws, cnt = _decode.workspace(dev, lib.fa_mla_workspace_bytes(n_slots, H_q, N_q, DV),
                                 lib.fa_mla_counters_len(B, H_q, N_q))
