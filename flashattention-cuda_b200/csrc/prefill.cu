@@ -17,10 +17,13 @@
 // The running maximum is only raised (and O rescaled) when it grew by more than 2^8, which keeps
 // P <= 256 in half precision and makes TMEM round trips of O rare.
 //
-// fp16 inputs: the exponentials run two per MUFU operation (ex2.approx.f16x2 on the half-precision
-// pair of scale * s - m); P is needed in half precision for the second MMA anyway, so nothing is rounded
-// twice, and the row sum is taken over the rounded P (pairwise in half precision over 8 values, then fp32).
-// bf16 inputs keep fp32 exponentials (a bf16 exponent argument would be too coarse).
+// Measured and not kept (B = 4, H = 32, N = 4096, d = 128 fp16; this kernel 660 us): two exponentials per
+// instruction (ex2.approx.f16x2 on the half-precision pair of scale * s - m) 662 us; two threads per query row
+// (four softmax warpgroups) 703 us; two 64-key score buffers per query tile so that the softmax threads never
+// wait for their own MMAs 856 us (N = 64 score MMAs re-read the query operand from shared memory twice as
+// often).  None of the three shortens the softmax threads' share, yet none helps, which points at the operand
+// traffic of the MMAs as the bound: per 128 x 128 step the Q, K and V tiles are read from shared memory (96 KB)
+// while TMA writes 32 KB, i.e. 128 KB per 1024 MMA cycles, the 128 B/clk an SM's shared memory delivers.
 //
 // Behaviour: the reference's dense entry point (fa_kernels/__init__.py:26-42,
 // kernels/v5_wmma/wmma_attention.cu:229-263).
@@ -82,23 +85,6 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   uint64_t r;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-// (lo, hi) fp32 -> packed half2, round to nearest; +-inf and out-of-range values become +-inf
-__device__ __forceinline__ uint32_t cvt_h2(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-// 2^x of both halves in one MUFU operation (half-precision result)
-__device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
-  uint32_t r;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(x));
-  return r;
-}
-__device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -285,42 +271,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_use, -m_use);
       // P as packed half-precision pairs: register c holds keys 2c, 2c+1
       uint32_t pk[64];
-      float sum;
-      if constexpr (BF16) {
-        uint64_t sums[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
+      uint64_t sums[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float x0, x1;
-          unpack2(fma2(pack2(s[2 * c], s[2 * c + 1]), sc2, nm2), x0, x1);
-          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-          sums[c & 3] = add2(sums[c & 3], pack2(e0, e1));
-          pk[c] = pack_bf2(e0, e1);
-        }
-        float sum_lo, sum_hi;
-        unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), sum_lo, sum_hi);
-        sum = sum_lo + sum_hi;
-      } else {
-        // two exponentials per MUFU operation; masked scores arrive as -inf and give +0
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float x0, x1;
-          unpack2(fma2(pack2(s[2 * c], s[2 * c + 1]), sc2, nm2), x0, x1);
-          pk[c] = ex2_h2(cvt_h2(x0, x1));
-        }
-        // row sum of the rounded P: three pairwise levels in half precision (8 values <= 2^8 each, exact to
-        // 2^-11 relative per level), the remaining 16 partial sums in fp32
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int g8 = 0; g8 < 8; ++g8) {
-          const uint32_t a0 = hadd2_u32(pk[8 * g8 + 0], pk[8 * g8 + 1]), a1 = hadd2_u32(pk[8 * g8 + 2], pk[8 * g8 + 3]);
-          const uint32_t a2 = hadd2_u32(pk[8 * g8 + 4], pk[8 * g8 + 5]), a3 = hadd2_u32(pk[8 * g8 + 6], pk[8 * g8 + 7]);
-          const uint32_t w = hadd2_u32(hadd2_u32(a0, a1), hadd2_u32(a2, a3));
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-          acc[g8 & 1] += f.x;
-          acc[2 + (g8 & 1)] += f.y;
-        }
-        sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      for (int c = 0; c < 64; ++c) {
+        float x0, x1;
+        unpack2(fma2(pack2(s[2 * c], s[2 * c + 1]), sc2, nm2), x0, x1);
+        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+        sums[c & 3] = add2(sums[c & 3], pack2(e0, e1));
+        pk[c] = BF16 ? pack_bf2(e0, e1) : pack_h2(e0, e1);
       }
+      float sum_lo, sum_hi;
+      unpack2(add2(add2(sums[0], sums[1]), add2(sums[2], sums[3])), sum_lo, sum_hi);
+      const float sum = sum_lo + sum_hi;
       l_run = l_run * alpha + sum;
       // S_FULL of key tile j implies P V of key tile j-1 has finished (same issuing thread, in order),
       // so O may be rescaled here
