@@ -478,7 +478,7 @@ int launch_mla(const MlaParams& p, int n_items, int row_tiles, cudaStream_t st) 
 }  // namespace fa
 
 namespace fa {
-// CTA-pair tensor-core path (mla_pair.cu)
+// CTA-pair tensor-core path (mla_pair.cu, mla_pair_f8.cu)
 bool mla_pair_applicable(const fa_mla_args* a);
 int mla_pair_max_pages();
 size_t mla_pair_workspace_bytes(int n_slots, int M);
@@ -537,8 +537,8 @@ extern "C" int fa_mla_decode_fwd(const fa_mla_args* a) {
   FA_CHECK_ARG(a->counters != nullptr, "counters must be non-null");
   if (a->counters_len < n_counters) return fail(FA_ERR_WORKSPACE, "counters hold %zu ints < %zu", a->counters_len, n_counters);
 
-  // bf16 (576, 512) latents on power-of-two pages >= 64 run on the CTA-pair tcgen05 kernel unless the caller
-  // asks for the fused mma.sync kernel (engine_hint 2) or a key range is too long for it
+  // bf16 and E4M3 (576, 512) latents on power-of-two pages >= 64 run on the CTA-pair tcgen05 kernels unless the
+  // caller asks for the fused mma.sync kernel (engine_hint 2) or a key range is too long for them
   if (a->engine_hint != 2 && mla_pair_applicable(a)) {
     if (a->workspace_bytes < mla_pair_workspace_bytes(a->n_slots, M))
       return fail(FA_ERR_WORKSPACE, "workspace %zu B < %zu B", a->workspace_bytes, mla_pair_workspace_bytes(a->n_slots, M));

@@ -52,11 +52,6 @@ struct PrefillParams {
 
 enum { P2_ERR_Q = 21, P2_ERR_KV_FULL = 22, P2_ERR_KV_EMPTY = 23, P2_ERR_S_FULL = 24, P2_ERR_P_READY = 25, P2_ERR_O_DONE = 26 };
 
-template <int NREG>
-__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
-template <int NREG>
-__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
-
 // 32 packed columns (64 half-precision values) of this thread's TMEM lane
 __device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(

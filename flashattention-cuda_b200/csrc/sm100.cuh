@@ -155,6 +155,12 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool bf16, bool a
          ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Per-warpgroup register budget (every thread of the four warps executes the same instruction).
+template <int NREG>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
+template <int NREG>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(NREG)); }
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

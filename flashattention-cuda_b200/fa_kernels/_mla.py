@@ -115,12 +115,15 @@ def mla_decode(q, l_pool, l_micro, block_table, page_size, n_k, kv_lora_rank, sc
     rows32 = 16 * ((H_q * N_q + 31) // 32)          # the planner counts 16-row tiles; this kernel uses 32
     tc_geometry = (DQK == 576 and DV == 512 and page_size % 64 == 0 and page_size & (page_size - 1) == 0
                    and engine_hint != 2)
-    # Quantised latents reach the tensor-core kernels through a bf16 copy of the tokens in use (one
-    # elementwise pass, fa_mla_expand_latent): worth it when the head rows fill an MMA tile and the copy
-    # fits the budget; otherwise the fused mma.sync kernel dequantises tile by tile.
-    expand = (tc_geometry and fmt in (FA_E4M3, FA_NVFP4) and H_q * N_q >= 64
+    # An FP8 latent of that geometry with enough head rows to fill an MMA tile runs on the tensor-core kernel
+    # as it is (tcgen05 kind::f8f6f4 on the stored bytes, csrc/mla_pair_f8.cu).  An NVFP4 latent reaches the
+    # tensor-core kernel through a transient bf16 copy of the tokens in use (one elementwise pass,
+    # fa_mla_expand_latent) when the copy fits the budget.  Everything else runs on the fused mma.sync kernel,
+    # which dequantises tile by tile.
+    fused_fp8 = tc_geometry and fmt == FA_E4M3 and H_q * N_q >= 64 and l_pool.data_ptr() % 16 == 0
+    expand = (tc_geometry and fmt == FA_NVFP4 and H_q * N_q >= 64
               and l_pool.shape[0] * page_size * DQK * 2 <= _expand_budget_bytes())
-    tc_shape = tc_geometry and (fmt == FA_BF16 or expand)
+    tc_shape = tc_geometry and (fmt == FA_BF16 or expand or fused_fp8)
     if tc_shape:
         # the tensor-core kernel stages a bounded number of block-table entries per CTA pair: bound the ranges
         cap = lib.fa_mla_pair_max_range(page_size)

@@ -305,10 +305,10 @@ typedef struct fa_mla_args {
   size_t counters_len;
   void* stream;
   int engine_hint;   /* 0 = choose (tcgen05 on a CTA pair where it applies); 2 = force the mma.sync kernel.
-                        The tcgen05 kernel needs a bf16 (576, 512) latent, page_size a power of two >= 64
-                        and key ranges <= fa_mla_pair_max_range; everything else (FP8 / NVFP4 latents read
-                        in place, the (160, 128) and (96, 64) geometries, other page sizes) runs on the
-                        mma.sync kernel */
+                        The tcgen05 kernels need a (576, 512) latent in bf16 (bf16 q) or E4M3 (fp16 q, pool
+                        16-byte aligned; per-token or per-tensor scales), page_size a power of two >= 64 and
+                        key ranges <= fa_mla_pair_max_range; everything else (NVFP4 latents read in place, the
+                        (160, 128) and (96, 64) geometries, other page sizes) runs on the mma.sync kernel */
 } fa_mla_args;
 FA_API size_t fa_mla_counters_len(int B, int H_q, int N_q);
 FA_API size_t fa_mla_workspace_bytes(int n_slots, int H_q, int N_q, int DV);
