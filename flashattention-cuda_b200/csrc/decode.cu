@@ -991,9 +991,19 @@ static int decode_check(const fa_decode_args* a) {
   return FA_OK;
 }
 
+namespace fa {
+// tcgen05 path for E4M3 pools (decode_tc.cu)
+bool decode_tc_applicable(const fa_decode_args* a);
+int launch_decode_tc(const fa_decode_args* a, cudaStream_t st);
+}  // namespace fa
+
 extern "C" int fa_paged_decode_fwd(const fa_decode_args* a) {
   const int rc_check = decode_check(a);
   if (rc_check != FA_OK) return rc_check;
+  // E4M3 pools on pages of 64 or more tokens, one query position, at most 8 heads per KV head: the keys become
+  // the M dimension of tcgen05 MMAs on the stored bytes (variant 9 keeps the mma.sync kernel)
+  if (a->variant != 9 && a->variant != 2 && fa::decode_tc_applicable(a))
+    return fa::launch_decode_tc(a, reinterpret_cast<cudaStream_t>(a->stream));
   const int fmt = a->kv_dtype == FA_F16 ? KV_F16 : a->kv_dtype == FA_BF16 ? KV_BF16 : a->kv_dtype == FA_E4M3 ? KV_E4M3 : KV_NVFP4;
   const int G = a->H_q / a->H_kv;
   const int M = G * a->N_q;

@@ -205,6 +205,10 @@ def paged_decode(q, k_pool, v_pool, block_table, page_size, n_k, scale, causal=F
     G = H_q // H_kv
     # the fp16 / bf16 kernel at d = 128 keeps three 32 KB stages per CTA: two CTAs per SM, the others three
     ctas = 2 if (kv_format in ("f16", "bf16") and d == 128) else 3
+    # E4M3 pools on pages >= 64 with one query position run on the tcgen05 kernel: one CTA per SM
+    if (kv_format == "e4m3" and d == 128 and N_q == 1 and G <= 8 and page_size >= 64
+            and page_size & (page_size - 1) == 0 and int(variant) not in (2, 9)):
+        ctas = 1
     items, n_items, n_slots, max_range, _ = plan(lens, n_max, B, H_kv, G * N_q, page_size, dev, int(chunk_hint), ctas)
     ws, cnt = workspace(dev, lib.fa_decode_workspace_bytes(n_slots, H_q, N_q, d),
                         lib.fa_decode_counters_len(B, H_q, H_kv, N_q))
