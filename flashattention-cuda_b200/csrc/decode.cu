@@ -1186,7 +1186,12 @@ extern "C" int fa_paged_decode_host(const fa_decode_host_args* h) {
   int n_items = 0, max_range = 0;
   // as the Python host does: the fp16 / bf16 kernel at d = 128 runs two CTAs per SM, the planner counts three
   const int sms = device_sm_count();
-  const int plan_sms = ((a.kv_dtype == FA_F16 || a.kv_dtype == FA_BF16) && a.D == 128) ? -2 * sms : sms;
+  int plan_sms = ((a.kv_dtype == FA_F16 || a.kv_dtype == FA_BF16) && a.D == 128) ? -2 * sms : sms;
+  {
+    fa_decode_args probe = a;        // the tcgen05 kernel for E4M3 pools keeps one CTA per SM
+    probe.max_range_keys = 0;
+    if (a.variant != 9 && a.variant != 2 && fa::decode_tc_applicable(&probe)) plan_sms = -sms;
+  }
   const int rc = fa_decode_plan(h->seq_lens_host, h->n_k, a.B, a.H_kv, (a.H_q / a.H_kv) * a.N_q, a.page_size, plan_sms,
                                 h->chunk_hint, h->items_host, h->max_items, &n_items, &max_range);
   if (rc != FA_OK) return rc;
