@@ -158,7 +158,10 @@ typedef struct fa_decode_args {
   int32_t* counters;
   size_t counters_len;
   void* stream;
-  int variant;         /* 0 = default kernel configuration; other values select tuning variants */
+  int variant;         /* 0 = the library chooses: E4M3 pools with D = 128 on power-of-two pages >= 64, N_q = 1 and
+                          H_q / H_kv <= 8 run on the tcgen05 kernel (keys as the M dimension, one CTA per SM: plan
+                          with num_sms = -SMs), everything else on the mma.sync kernel; 9 = always the mma.sync
+                          kernel; 1, 2 = tuning variants of the mma.sync kernel */
 } fa_decode_args;
 
 FA_API size_t fa_decode_workspace_bytes(int n_slots, int H_q, int N_q, int D);
