@@ -215,6 +215,48 @@ def test_fp8_decode_per_token_scales(G, d):
     assert_close(out, ref, what="fp8 per-token")
 
 
+@pytest.mark.parametrize("per_token", [False, True])
+@pytest.mark.parametrize("G", [1, 4, 5, 8])
+def test_fp8_tcgen05_and_mma_sync_kernels_agree(G, per_token):
+    """Pages of 64 tokens and one query position put E4M3 pools on the tcgen05 kernel (keys as the M dimension,
+    csrc/decode_tc.cu); variant=9 keeps the mma.sync kernel.  Both against the oracle, on ragged per-sequence
+    lengths that cover less than one tile (100 keys), a tile boundary (128), an odd tile count, a long sequence
+    that is split into key ranges, and a causal limit inside the sequence."""
+    from fa_kernels import fp8_attention
+    H_kv, d, page_size = 2, 128, 64
+    lens = [100, 128, 129, 1000, 9001]
+    B, N_max = len(lens), max(lens)
+    q_t, q, k, v = _fp8_case(B, H_kv, G, N_max, d, page_size, 77 + G, per_token)
+    k[..., 9] *= 10.0
+    if per_token:
+        kb, ks = O.quantize_fp8_e4m3_per_token(k)
+        vb, vs = O.quantize_fp8_e4m3_per_token(v)
+        k_hat, v_hat = O.e4m3_decode(kb) * ks[..., None], O.e4m3_decode(vb) * vs[..., None]
+    else:
+        kb, sk = O.quantize_fp8_e4m3(k)
+        vb, sv = O.quantize_fp8_e4m3(v)
+        k_hat, v_hat = O.dequantize_fp8_e4m3(kb, sk), O.dequantize_fp8_e4m3(vb, sv)
+    perm = perm_for(B * ((N_max + page_size - 1) // page_size), 77)
+    kp, vp, bt, _ = O.build_paged_kv(kb, vb, page_size, perm)
+    if per_token:
+        ksp, vsp, _, _ = O.build_paged_kv(ks[..., None], vs[..., None], page_size, perm)
+        scales = (dev(ksp[..., 0]), dev(vsp[..., 0]))
+    else:
+        scales = (sk, sv)
+    for causal, q_off in ((False, 0), (True, 70)):
+        outs = {}
+        for variant in (0, 9):
+            out, lse = fp8_attention(q_t.cuda(), dev(kp), dev(vp), dev(bt), page_size, lens, *scales, causal=causal,
+                                     q_offset=q_off, return_lse=True, variant=variant)
+            outs[variant] = out
+            for b, n in enumerate(lens):
+                n_eff = min(n, q_off + 1) if causal else n
+                ref, ref_lse = O.gqa_attention_ref(q[b:b + 1], k_hat[b:b + 1, :, :n_eff], v_hat[b:b + 1, :, :n_eff], return_lse=True)
+                assert_close(out[b:b + 1], ref, what=f"fp8 variant {variant} seq {b} causal {causal}")
+                np.testing.assert_allclose(lse[b:b + 1].cpu().numpy(), ref_lse, atol=3e-3, rtol=1e-3)
+        assert_close(outs[0], outs[9].cpu().numpy(), what="tcgen05 vs mma.sync")
+
+
 # -------------------------------------------------------------------------------------------- NVFP4
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("N_k", [4096, 8190])
