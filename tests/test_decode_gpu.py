@@ -257,6 +257,33 @@ def test_fp8_tcgen05_and_mma_sync_kernels_agree(G, per_token):
         assert_close(outs[0], outs[9].cpu().numpy(), what="tcgen05 vs mma.sync")
 
 
+def test_fp8_tcgen05_rising_scores_and_zero_tokens():
+    """Scores that keep rising along the sequence (the running maximum is raised in many tiles, so the output
+    accumulator is rescaled again and again), queries eight times the usual magnitude, and tokens whose K and V
+    rows are all zero (their per-token scale is the quantiser's floor): tcgen05 and mma.sync kernels against
+    the oracle."""
+    from fa_kernels import fp8_attention
+    B, H_kv, G, N_k, d, page_size = 2, 2, 4, 6000, 128, 64
+    q_t, q, k, v = _fp8_case(B, H_kv, G, N_k, d, page_size, 123, True)
+    q_t, q = q_t * 8.0, q * 8.0
+    ramp = np.linspace(0.0, 1.0, N_k, dtype=np.float32)[None, None, :, None]
+    k = k * 0.05 + ramp * np.sign(q[:, ::G, :1, :]) * 0.5            # the dot product with q grows with the position
+    k[:, :, 100:140] = 0.0
+    v[:, :, 100:140] = 0.0
+    v[:, :, 4000:4003] = 0.0
+    kb, ks = O.quantize_fp8_e4m3_per_token(k)
+    vb, vs = O.quantize_fp8_e4m3_per_token(v)
+    perm = perm_for(B * ((N_k + page_size - 1) // page_size), 123)
+    kp, vp, bt, _ = O.build_paged_kv(kb, vb, page_size, perm)
+    ksp, vsp, _, _ = O.build_paged_kv(ks[..., None], vs[..., None], page_size, perm)
+    ref, ref_lse = O.gqa_attention_ref(q, O.e4m3_decode(kb) * ks[..., None], O.e4m3_decode(vb) * vs[..., None], return_lse=True)
+    for variant in (0, 9):
+        out, lse = fp8_attention(q_t.cuda(), dev(kp), dev(vp), dev(bt), page_size, N_k, dev(ksp[..., 0]), dev(vsp[..., 0]),
+                                 return_lse=True, variant=variant)
+        assert_close(out, ref, what=f"fp8 rising scores, variant {variant}")
+        np.testing.assert_allclose(lse.cpu().numpy(), ref_lse, atol=3e-3, rtol=1e-3)
+
+
 # -------------------------------------------------------------------------------------------- NVFP4
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("N_k", [4096, 8190])
