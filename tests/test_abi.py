@@ -93,6 +93,7 @@ def test_planner_candidates_cover_every_sequence_once():
         ([8192] * 37, 0, 8, 4, 16, -296), ([8192] * 45, 0, 8, 4, 16, -296), ([8192] * 80, 0, 8, 4, 16, -296),
         (None, 1048576, 8, 4, 64, 148), ([131072], 0, 1, 1, 256, -296), ([5, 70000, 0, 64, 4097], 0, 2, 16, 16, 148),
         ([300] * 1000, 0, 8, 4, 16, 148),
+        (None, 1048576, 8, 4, 64, -148), ([100, 128, 129, 1000, 9001], 0, 2, 4, 64, -148),      # one CTA per SM (tcgen05 decode)
     ]
     kinds = set()
     for lens, n_k, H_kv, rows, page, sms in shapes:
