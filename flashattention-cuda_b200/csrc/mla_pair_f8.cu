@@ -28,7 +28,7 @@
 //                the scores of the tile it is overwritten with this CTA's columns of the peer's keys when
 //                d & 1 != r, so block parity = key half in both CTAs and one descriptor serves the pair.
 //
-//   memory       per CTA, shared: two tile buffers (2 x 40 KB), two P buffers (two pieces of 64 rows x 128 keys,
+//   memory       per CTA, shared: three tile buffers (3 x 40 KB), two P buffers (two pieces of 64 rows x 128 keys,
 //                32 KB), the second query pieces (40 KB) and the first pieces of the rope dims (8 KB).  Tensor
 //                memory: O (256 columns), two score buffers (2 x 64), and the first query pieces of dims
 //                [0, 512) as the A operand (128 columns, four dims per column), which takes their reads off
@@ -57,6 +57,7 @@ constexpr float kFThreshold = 4.f;            // the running maximum is followed
 constexpr float kFPre = 4.f;                  // weights go to the tensor core times 2^4
 constexpr int kFThreads = 384;                // 4 producer / issuer warps + 8 softmax warps
 constexpr int kFSoft = 256;                   // softmax threads
+constexpr int kFTiles = 3;                    // tile buffers (score and P buffers: two)
 
 __device__ __forceinline__ void mma2_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
   asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
@@ -102,11 +103,13 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
   uint8_t* sQ = smem;                          // second pieces: [5 blocks][64 rows][128 dims]
   uint8_t* sQr = sQ + kFBlocks * kPBlk;        // first pieces of the rope dims: one block laid out like block 4
   uint8_t* sP = sQr + kPBlk;                   // [2 tiles][2 pieces][64 rows][128 keys]
-  uint8_t* sT = sP + 4 * kPBlk;                // [2 tiles][5 blocks][64 keys][128 dims]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sT + 2 * kFBlocks * kPBlk);
-  enum { QT_READY = 0, X_FULL = 1, X_FULLB = 3, R_FULL = 5, S_FULL = 7, T_FREEA = 9, T_FREE = 11, P_READY = 13, SC_READY = 15,
-         Z_GO = 19, NBARS = 20 };
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 20);
+  uint8_t* sT = sP + 4 * kPBlk;                // [3 tiles][5 blocks][64 keys][128 dims]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sT + kFTiles * kFBlocks * kPBlk);
+  // tile buffers and their barriers (X_FULL, X_FULLB, R_FULL, T_FREEA, T_FREE) are indexed by j % 3, score and P
+  // buffers (S_FULL, P_READY) by j & 1, scale buffers by j & 3
+  enum { QT_READY = 0, X_FULL = 1, X_FULLB = 4, R_FULL = 7, T_FREEA = 10, T_FREE = 13, S_FULL = 16, P_READY = 18, SC_READY = 20,
+         Z_GO = 24, NBARS = 25 };
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 26);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   int* s_ticket = const_cast<int*>(reinterpret_cast<volatile int*>(s_tmem + 2));
   float* s_red = reinterpret_cast<float*>(s_tmem + 4);             // [2][256]
@@ -142,13 +145,15 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
   if (threadIdx.x == 0) {
     *s_abort = 0;
     mbar_init(bar(QT_READY), 2 * kFSoft);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kFTiles; ++i) {
       mbar_init(bar(X_FULL + i), 1);
       mbar_init(bar(X_FULLB + i), 1);
       mbar_init(bar(R_FULL + i), 1);
-      mbar_init(bar(S_FULL + i), 1);
       mbar_init(bar(T_FREEA + i), 1);
       mbar_init(bar(T_FREE + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(S_FULL + i), 1);
       mbar_init(bar(P_READY + i), 2 * kFSoft);
     }
     for (int i = 0; i < 4; ++i) mbar_init(bar(SC_READY + i), 32);     // this CTA's scale loader warp
@@ -193,21 +198,21 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
       // ------------------------------------------------- TMA producer of the score operand (both CTAs)
-      // tile j -> buffer j & 1.  Blocks 0, 1 are released by the first half of the P V of the tile that used
+      // tile j -> buffer j % 3.  Blocks 0, 1 are released by the first half of the P V of the tile that used
       // the buffer, the others by the second half; the scores start on blocks 0, 1.
       for (int j = 0; j < n_tiles; ++j) {
-        const int bf = j & 1;
+        const int bf = j % kFTiles, use = j / kFTiles;           // tile buffer and how often it has been used
         const int tok_own = token_of(k_begin + j * 128 + 64 * (int)rank);
-        if (j >= 2 && !mbar_wait(bar(T_FREEA + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
+        if (j >= kFTiles && !mbar_wait(bar(T_FREEA + bf), (use - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
         const uint32_t xa_full0 = map_to_cta(bar(X_FULL + bf), 0), xb_full0 = map_to_cta(bar(X_FULLB + bf), 0);
         if (rank == 0) mbar_expect_tx(bar(X_FULL + bf), 2 * 2 * kPBlk);
         for (int d = 0; d < 2; ++d) tma_pair_2d(smem_u32(sT + (bf * kFBlocks + d) * kPBlk), &map_l, block_x(d), tok_own, xa_full0);
-        if (j >= 2 && !mbar_wait(bar(T_FREE + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
+        if (j >= kFTiles && !mbar_wait(bar(T_FREE + bf), (use - 1) & 1, s_abort, p.status, P2_ERR_X_EMPTY)) break;
         if (rank == 0) mbar_expect_tx(bar(X_FULLB + bf), 2 * 3 * kPBlk);
         for (int d = 2; d < kFBlocks; ++d) tma_pair_2d(smem_u32(sT + (bf * kFBlocks + d) * kPBlk), &map_l, block_x(d), tok_own, xb_full0);
-        // pull the tile after the next one into L2 while there is no buffer for it yet
-        if (j + 2 < n_tiles) {
-          const int tok_pf = token_of(k_begin + (j + 2) * 128 + 64 * (int)rank);
+        // pull the first tile that has no buffer yet into L2
+        if (j + kFTiles < n_tiles) {
+          const int tok_pf = token_of(k_begin + (j + kFTiles) * 128 + 64 * (int)rank);
           if (tok_pf < p.total_tokens)
             for (int d = 0; d < kFBlocks; ++d) tma_prefetch_l2_2d(&map_l, block_x(d), tok_pf);
         }
@@ -247,10 +252,10 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
         mbar_arrive(bar(SC_READY + (j & 3)));
       };
       auto tile_step = [&](int j, float (&nxt)[4]) -> bool {        // nxt: the scales of tile j + 1
-        const int bf = j & 1;
+        const int bf = j % kFTiles;
         bool ok = true;
         if (lane == 0) {
-          ok = mbar_wait(bar(S_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_S_FULL);
+          ok = mbar_wait(bar(S_FULL + (j & 1)), (j >> 1) & 1, s_abort, p.status, P2_ERR_S_FULL);
           if (ok) {
             const uint32_t r_full0 = map_to_cta(bar(R_FULL + bf), 0);
             if (rank == 0) mbar_expect_tx(bar(R_FULL + bf), 2 * 2 * kPBlk);
@@ -288,19 +293,19 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
       bool ok = mbar_wait(bar(QT_READY), 0, s_abort, p.status, P2_ERR_QT);
       auto step_off = [](int t) { return t < 16 ? (t >> 2) * kPBlk + (t & 3) * 32 : 4 * kPBlk + 64 + (t - 16) * 32; };
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int bf = j & 1;
-        if (j >= 2) ok = mbar_wait(bar(P_READY + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_P_READY);
-        if (ok) ok = mbar_wait(bar(X_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
+        const int sb = j & 1, tb = j % kFTiles, use = j / kFTiles;   // score buffer; tile buffer and its use count
+        if (j >= 2) ok = mbar_wait(bar(P_READY + sb), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_P_READY);
+        if (ok) ok = mbar_wait(bar(X_FULL + tb), use & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t_base = smem_u32(sT + bf * kFBlocks * kPBlk), q_base = smem_u32(sQ), d_s = tm_s + 64 * bf;
+        const uint32_t t_base = smem_u32(sT + tb * kFBlocks * kPBlk), q_base = smem_u32(sQ), d_s = tm_s + 64 * sb;
         const uint32_t qr_base = smem_u32(sQr) - 4 * kPBlk;          // so that step_off(16), step_off(17) land in sQr
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
           mma2_f8_ts(d_s, tm_q + 8 * t, smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, t > 0 ? 1u : 0u);
           mma2_f8(d_s, smem_desc_sw128(q_base + step_off(t), 16, 1024), smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, 1u);
         }
-        ok = mbar_wait(bar(X_FULLB + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
+        ok = mbar_wait(bar(X_FULLB + tb), use & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -311,7 +316,7 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
             mma2_f8(d_s, smem_desc_sw128(qr_base + step_off(t), 16, 1024), smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, 1u);
           mma2_f8(d_s, smem_desc_sw128(q_base + step_off(t), 16, 1024), smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, 1u);
         }
-        mma2_commit_both(bar(S_FULL + bf));
+        mma2_commit_both(bar(S_FULL + sb));
       }
     }
   } else if (warp == 3) {
@@ -322,8 +327,8 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
       constexpr uint32_t idesc_pv = idesc_f16(128, 256, false, false, true);
       bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int bf = j & 1;
-        ok = mbar_wait(bar(R_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_Y_FULL);
+        const int sb = j & 1, tb = j % kFTiles, use = j / kFTiles;
+        ok = mbar_wait(bar(R_FULL + tb), use & 1, s_abort, p.status, P2_ERR_Y_FULL);
         if (!ok) break;
         if (ragged_end && j + 1 == n_tiles) {
           // everything of the last tile has landed in both CTAs: let the softmax threads clear the value
@@ -331,10 +336,10 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
           mbar_arrive(bar(Z_GO));
           mbar_arrive_cluster(map_to_cta(bar(Z_GO), 1));
         }
-        ok = mbar_wait(bar(P_READY + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_P_READY);
+        ok = mbar_wait(bar(P_READY + sb), (j >> 1) & 1, s_abort, p.status, P2_ERR_P_READY);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t_base = smem_u32(sT + bf * kFBlocks * kPBlk), p_base = smem_u32(sP + bf * 2 * kPBlk);
+        const uint32_t t_base = smem_u32(sT + tb * kFBlocks * kPBlk), p_base = smem_u32(sP + sb * 2 * kPBlk);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
 #pragma unroll
@@ -346,7 +351,7 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
                       smem_desc_sw128(t_base + (2 * s + h) * kPBlk + kk * 4096, kPBlk, 1024), idesc_pv,
                       (j > 0 || hk > 0 || pc > 0) ? 1u : 0u);
           }
-          mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
+          mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + tb));
         }
       }
     }
@@ -510,7 +515,7 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
       // O may only be rescaled between two P V: this tile's is not issued before P arrives, the previous
       // one has to be waited for (rare after the first tiles).  Each warpgroup rescales half of the columns.
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        ok = mbar_wait(bar(T_FREE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
+        ok = mbar_wait(bar(T_FREE + ((j - 1) % kFTiles)), ((j - 1) / kFTiles) & 1, s_abort, p.status, P2_ERR_PV_DONE);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -523,6 +528,12 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
           tmem_st32(tm_o + lane_base + (4 * hh + c) * 32, o);
         }
         tmem_wait_st();
+      }
+      // the P buffer of tile j - 2 has been read once its P V is done (with three tile buffers the scores of
+      // tile j no longer wait for that)
+      if (j >= 2) {
+        ok = mbar_wait(bar(T_FREE + ((j - 2) % kFTiles)), ((j - 2) / kFTiles) & 1, s_abort, p.status, P2_ERR_PV_DONE);
+        if (!ok) break;
       }
       // this thread's 32 weights -> bytes [32 part, + 32) of row `row` of the two P pieces (16-byte chunks
       // swizzled by the row)
@@ -545,7 +556,7 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
         const int blk = tid_sm >> 6;                   // 4 value blocks, 64 threads each
         const int kr = tid_sm & 63;
         if (k0 + 64 * (blk & 1) + kr >= k_end) {
-          uint4* d = reinterpret_cast<uint4*>(sT + (bf * kFBlocks + blk) * kPBlk + kr * 128);
+          uint4* d = reinterpret_cast<uint4*>(sT + ((j % kFTiles) * kFBlocks + blk) * kPBlk + kr * 128);
 #pragma unroll
           for (int i = 0; i < 8; ++i) d[i] = make_uint4(0, 0, 0, 0);
         }
@@ -555,7 +566,7 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
       mbar_arrive_peer(map_to_cta(bar(P_READY + bf), 0));
     }
     if (ok && n_tiles > 0)
-      ok = mbar_wait(bar(T_FREE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, s_abort, p.status, P2_ERR_PV_DONE);
+      ok = mbar_wait(bar(T_FREE + ((n_tiles - 1) % kFTiles)), ((n_tiles - 1) / kFTiles) & 1, s_abort, p.status, P2_ERR_PV_DONE);
     // the four threads of a row add up their sums (the tile loop's last use of this half of s_red is two tiles back)
     float* red = s_red + (n_tiles & 1) * 256;
     red[64 * part + row] = l_run;
@@ -649,9 +660,9 @@ int launch_mla_pair_f8(const fa_mla_args* a, cudaStream_t st) {
   p.causal = a->causal; p.q_offset = a->q_offset; p.out_dtype = a->out_dtype;
   p.tok_scale = a->l_token_scale;
   p.tensor_scale = a->l_scale;
-  constexpr int SMEM = (kFBlocks + 1 + 4 + 2 * kFBlocks) * kPBlk + 12288 + 1024;
+  constexpr int SMEM = (kFBlocks + 1 + 4 + kFTiles * kFBlocks) * kPBlk + 12288 + 1024;
   static_assert(SMEM <= 227 * 1024, "MLA FP8 pair tile does not fit shared memory");
-  static_assert(20 * 8 + 16 + 2048 + 4 * 3 * 128 * 4 + kPMaxPages * 4 <= 12288, "barriers, scratch, token scales and block table exceed their 12 KB");
+  static_assert(26 * 8 + 16 + 2048 + 4 * 3 * 128 * 4 + kPMaxPages * 4 <= 12288, "barriers, scratch, token scales and block table exceed their 12 KB");
   static int configured_device = -1;
   int dev = 0;
   FA_CUDA_OK(cudaGetDevice(&dev));
