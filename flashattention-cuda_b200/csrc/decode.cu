@@ -1168,9 +1168,13 @@ extern "C" int fa_paged_decode_host(const fa_decode_host_args* h) {
   FA_CHECK_ARG(a.B >= 1 && a.H_kv >= 1 && a.H_q >= 1 && a.N_q >= 1 && a.H_q % a.H_kv == 0, "fa_paged_decode_host: bad B/H/N_q");
   FA_CHECK_ARG(a.page_size >= 1 && a.n_logical >= 1 && a.num_blocks >= 1, "fa_paged_decode_host: bad page_size / n_logical / num_blocks");
   FA_CHECK_ARG(h->block_table_bytes >= (size_t)a.B * a.n_logical * sizeof(int32_t), "fa_paged_decode_host: block_table_host smaller than [B, n_logical]");
-  // The table is in host memory here, so a bad entry is refused before anything is enqueued (the kernel
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a.stream);
+  FA_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a.q), h->q_host, h->q_bytes, cudaMemcpyHostToDevice, st));
+  FA_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(a.block_table), h->block_table_host, h->block_table_bytes, cudaMemcpyHostToDevice, st));
+  // The table is in host memory here, so a bad entry is refused before any kernel is launched (the kernel
   // would mask the page and raise its status flag; the reference's host checks are of the same kind,
-  // kernels/v8_gqa_ss/gqa_ss_attention.cu:267-291).
+  // kernels/v8_gqa_ss/gqa_ss_attention.cu:267-291).  The scan runs while the two copies above are in flight; a
+  // refused call leaves the staging buffers overwritten and nothing else.
   for (int b = 0; b < a.B; ++b) {
     const int len = h->seq_lens_host ? h->seq_lens_host[b] : h->n_k;
     FA_CHECK_ARG(len >= 0, "fa_paged_decode_host: negative sequence length at b=%d", b);
@@ -1180,9 +1184,6 @@ extern "C" int fa_paged_decode_host(const fa_decode_host_args* h) {
     for (int64_t j = 0; j < pages; ++j)
       FA_CHECK_ARG((uint32_t)row[j] < (uint32_t)a.num_blocks, "fa_paged_decode_host: block_table[%d][%lld] = %d is outside [0, %d)", b, (long long)j, row[j], a.num_blocks);
   }
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(a.stream);
-  FA_CUDA_OK(cudaMemcpyAsync(const_cast<void*>(a.q), h->q_host, h->q_bytes, cudaMemcpyHostToDevice, st));
-  FA_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(a.block_table), h->block_table_host, h->block_table_bytes, cudaMemcpyHostToDevice, st));
   int n_items = 0, max_range = 0;
   // as the Python host does: the fp16 / bf16 kernel at d = 128 runs two CTAs per SM, the planner counts three
   const int sms = device_sm_count();

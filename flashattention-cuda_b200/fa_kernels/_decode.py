@@ -363,8 +363,11 @@ class HostDecodeStep:
         h.chunk_hint = int(chunk_hint)
         h.dev.q_offset = int(q_offset)
         h.dev.stream = stream.cuda_stream
-        with torch.cuda.device(self.dev):
+        if torch.cuda.current_device() == self.dev.index:      # the usual case: no device switch on the step's path
             _lib.check(self.lib.fa_paged_decode_host(C.byref(h)), "fa_paged_decode_host")
+        else:
+            with torch.cuda.device(self.dev):
+                _lib.check(self.lib.fa_paged_decode_host(C.byref(h)), "fa_paged_decode_host")
         if self.items_done[i] is None:
             self.items_done[i] = torch.cuda.Event()
         self.items_done[i].record(stream)
