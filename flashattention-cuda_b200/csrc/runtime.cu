@@ -45,6 +45,7 @@ extern "C" const char* fa_status_text(int status_word) {
     case 24: wait = "dense attention: wait for the scores timed out"; break;
     case 25: wait = "dense attention: wait for P timed out"; break;
     case 26: wait = "dense attention: wait for the last P V timed out"; break;
+    case 27: wait = "dense attention: wait for the query buffers to drain timed out"; break;
     case 41: case 42: wait = "MLA pair kernel: wait for the query operand timed out"; break;
     case 43: case 44: wait = "MLA pair kernel: wait on a score-operand tile buffer timed out"; break;
     case 45: case 46: wait = "MLA pair kernel: wait on a value-operand tile buffer timed out"; break;
