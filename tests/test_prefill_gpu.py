@@ -3,7 +3,9 @@
 Shape matrix of the reference's dense tests (tests/test_correctness.py:30-37, 110-141 there: six
 shapes incl. partial tiles N=130 / N=100, both mask modes, explicit scale) plus N_q != N_k, bf16, LSE,
 the CPU-plumbing configuration (B=2 H=8 N=512 d=64, seed 0, checked against the committed sample of
-the reference's own output) and the full-size fp16 causal prefill configuration on sampled heads."""
+the reference's own output), the full-size fp16 causal prefill configuration on sampled heads, and every
+work-unit mode of the persistent launch (all heads compared with an fp32 torch reference, tolerance per output type
+written in the test)."""
 
 from __future__ import annotations
 
@@ -125,3 +127,46 @@ def test_full_size_causal_prefill_sampled_heads():
         ref = O.attention_ref(q[b:b + 1, h:h + 1].float().cpu().numpy(), k[b:b + 1, h:h + 1].float().cpu().numpy(),
                               v[b:b + 1, h:h + 1].float().cpu().numpy(), causal=True)
         assert_close(out[b:b + 1, h:h + 1], ref, what=f"config 2 head {b},{h}")
+
+
+def _torch_attention_fp32(q, k, v, causal):
+    """Plain fp32 softmax(q k^T / sqrt(d)) v on the GPU, head by head (the same mathematics as
+    oracle.fa_oracle.attention_ref; used where the oracle's numpy loops would take minutes)."""
+    B, H, N_q, d = q.shape
+    N_k = k.shape[2]
+    out = torch.empty(B, H, N_q, d, device=q.device, dtype=torch.float32)
+    mask = None
+    if causal:
+        mask = torch.arange(N_k, device=q.device)[None, :] > torch.arange(N_q, device=q.device)[:, None]
+    for b in range(B):
+        for h in range(H):
+            s = (q[b, h].float() @ k[b, h].float().T) / d ** 0.5
+            if causal:
+                s = s.masked_fill(mask, float("-inf"))
+            out[b, h] = torch.softmax(s, dim=-1) @ v[b, h].float()
+    return out
+
+
+@pytest.mark.parametrize("B,H,N_q,N_k,d,causal,out_dtype", [
+    (2, 80, 1280, 1280, 128, True, torch.float16),    # 160 heads x 5 tile pairs: paired units (3 per head, the middle one single)
+    (1, 160, 1100, 1100, 64, True, torch.float32),    # paired, last query tile partial, fp32 output (four store passes)
+    (1, 8, 2000, 2000, 128, True, torch.bfloat16),    # 64 items < SM count: one item per CTA, partial last tile
+    (3, 50, 300, 300, 64, False, torch.float16),      # 300 items on 148 CTAs, unpaired, second query tile mostly empty
+    (1, 200, 130, 700, 128, False, torch.float32),    # 200 one-tile items, second query tile holds 2 rows
+])
+def test_persistent_walk_modes_against_torch_fp32(B, H, N_q, N_k, d, causal, out_dtype):
+    """Every work-unit mode of the persistent launch: all heads and rows are compared, so a unit that is
+    skipped, done twice or written to the wrong rows cannot hide."""
+    from fa_kernels import attention
+    g = torch.Generator(device="cuda").manual_seed(N_q + H)
+    dt = torch.bfloat16 if out_dtype == torch.bfloat16 else torch.float16
+    q = torch.randn(B, H, N_q, d, device="cuda", generator=g).to(dt)
+    k = torch.randn(B, H, N_k, d, device="cuda", generator=g).to(dt)
+    v = torch.randn(B, H, N_k, d, device="cuda", generator=g).to(dt)
+    out, lse = attention(q, k, v, causal=causal, out_dtype=out_dtype, return_lse=True)
+    _status_ok()
+    ref = _torch_attention_fp32(q, k, v, causal)
+    tol = 2e-3 if out_dtype == torch.float32 else (2e-2 if out_dtype == torch.bfloat16 else 4e-3)
+    err = (out.float() - ref).abs().amax(dim=(2, 3))
+    assert float(err.max()) < tol, f"max |diff| {float(err.max()):.3e} at (b, h) {divmod(int(err.argmax()), H)}"
+    assert torch.isfinite(lse).all()
