@@ -137,6 +137,23 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
+// MMA with the two 32-bit words of each shared-memory descriptor given separately: the issuing thread keeps one low
+// word per operand buffer and adds a constant per k step, instead of assembling 64-bit descriptors per MMA.
+template <bool ACC>
+__device__ __forceinline__ void mma_ss_words(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc) {
+  asm volatile(
+      "{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n .reg .b64 db;\n setp.ne.b32 p, %5, 0;\n mov.b64 db, {%2, %3};\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kP2Threads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -227,24 +244,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, BF16, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(128, D, BF16, false, true);
-      auto issue_qk = [&](int i, int gt) {              // gt: ring position of the key tile
-        const int s = gt % STAGES;
+      // low descriptor words of the operand buffers (address >> 4 in bits 0-13, leading byte offset >> 4 in bits
+      // 16-29) and the high word all of them share (stride 1024 >> 4, descriptor version, 128-byte swizzle)
+      const uint32_t hi_w = (1024u >> 4) | (1u << 14) | (2u << 29);
+      uint32_t q_lo[2], k_lo[STAGES], v_lo[STAGES];
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * BLK_BYTES + (k & 3) * 32;
-          mma_f16_ss(tmem + i * 128, smem_desc_sw128(smem_u32(sQ + i * TILE_BYTES) + off, 16, 1024),
-                     smem_desc_sw128(smem_u32(sK + s * TILE_BYTES) + off, 16, 1024), idesc_qk, k > 0);
+      for (int i = 0; i < 2; ++i) q_lo[i] = ((smem_u32(sQ + i * TILE_BYTES) & 0x3ffffu) >> 4) | ((16u >> 4) << 16);
+#pragma unroll
+      for (int st = 0; st < STAGES; ++st) {
+        k_lo[st] = ((smem_u32(sK + st * TILE_BYTES) & 0x3ffffu) >> 4) | ((16u >> 4) << 16);
+        v_lo[st] = ((smem_u32(sV + st * TILE_BYTES) & 0x3ffffu) >> 4) | (((uint32_t)BLK_BYTES >> 4) << 16);
+      }
+      auto issue_qk = [&](int i, int gt) {              // gt: ring position of the key tile
+        const uint32_t a0 = q_lo[i], b0 = k_lo[gt % STAGES], d = tmem + i * 128;
+        mma_ss_words<false>(d, a0, b0, hi_w, idesc_qk);
+#pragma unroll
+        for (int k = 1; k < D / 16; ++k) {
+          const uint32_t off = ((k >> 2) * BLK_BYTES + (k & 3) * 32) >> 4;
+          mma_ss_words<true>(d, a0 + off, b0 + off, hi_w, idesc_qk);
         }
         mma_commit(bar(S_FULL + i));
       };
       auto issue_pv = [&](int i, int gt, bool first) {
-        const int s = gt % STAGES;
+        // A = P_i in tensor memory: 16 keys = 8 packed columns; B = V [128 keys][D], MN-major
+        const uint32_t b0 = v_lo[gt % STAGES], d = tmem + 256 + i * 128, a = tmem + i * 128;
+        mma_ts_words(d, a, b0, hi_w, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          // A = P_i in tensor memory: 16 keys = 8 packed columns; B = V [128 keys][D], MN-major
-          const uint64_t b_desc = smem_desc_sw128(smem_u32(sV + s * TILE_BYTES) + k * 2048, BLK_BYTES, 1024);
-          mma_f16_ts(tmem + 256 + i * 128, tmem + i * 128 + k * 8, b_desc, idesc_pv, (!first || k > 0) ? 1u : 0u);
-        }
+        for (int k = 1; k < 8; ++k) mma_ts_words(d, a + k * 8, b0 + (k * 2048 >> 4), hi_w, idesc_pv, 1u);
       };
       ItemWalk walk;
       int bh, qt, n_t[2];
