@@ -244,6 +244,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, BF16, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(128, D, BF16, false, true);
+      // a wait whose barrier is usually complete already costs one instruction here; the bounded wait with its
+      // abort-flag and clock reads is entered only when the first try fails
+      auto wait = [&](int b, int parity, int code) {
+        return mbar_try_wait(bar(b), parity) || mbar_wait(bar(b), parity, s_abort, p.status, code);
+      };
       // low descriptor words of the operand buffers (address >> 4 in bits 0-13, leading byte offset >> 4 in bits
       // 16-29) and the high word all of them share (stride 1024 >> 4, descriptor version, 128-byte swizzle)
       const uint32_t hi_w = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -280,8 +285,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int it = 0; ok && walk.next(p, bh, qt); ++it) {
         tiles_of(qt * 256, n_t);
         const int n_max = max(n_t[0], n_t[1]);
-        ok = mbar_wait(bar(Q_FULL), it & 1, s_abort, p.status, P2_ERR_Q) &&
-             mbar_wait(bar(KV_FULL + (g % STAGES)), (g / STAGES) & 1, s_abort, p.status, P2_ERR_KV_FULL);
+        ok = wait(Q_FULL, it & 1, P2_ERR_Q) &&
+             wait(KV_FULL + (g % STAGES), (g / STAGES) & 1, P2_ERR_KV_FULL);
         if (!ok) break;
         tc_fence_after();
         // S_i is free: the P V of the previous item's last key tile was issued before this by the same thread.
@@ -292,14 +297,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (n_max == 1) mma_commit(bar(Q_EMPTY));
         for (int j = 0; ok && j < n_max; ++j) {
           const int gt = g + j;
-          if (j + 1 < n_max) {
-            ok = mbar_wait(bar(KV_FULL + ((gt + 1) % STAGES)), ((gt + 1) / STAGES) & 1, s_abort, p.status, P2_ERR_KV_FULL);
-            if (!ok) break;
-          }
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             if (j < n_t[i]) {
-              ok = mbar_wait(bar(P_READY + i), n_p[i] & 1, s_abort, p.status, P2_ERR_P_READY);
+              ok = wait(P_READY + i, n_p[i] & 1, P2_ERR_P_READY);
               if (!ok) break;
               ++n_p[i];
               tc_fence_after();
@@ -307,6 +308,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               if (j + 1 == n_t[i]) mma_commit(bar(O_DONE + i));
             }
             if (i == 1) mma_commit(bar(KV_EMPTY + (gt % STAGES)));
+            if (i == 0 && j + 1 < n_max) {   // the next key tile is only needed from here on
+              ok = wait(KV_FULL + ((gt + 1) % STAGES), ((gt + 1) / STAGES) & 1, P2_ERR_KV_FULL);
+              if (!ok) break;
+              tc_fence_after();
+            }
             if (j + 1 < n_t[i]) issue_qk(i, gt + 1);
           }
           if (ok && j + 2 == n_max) mma_commit(bar(Q_EMPTY));   // the item's last score MMAs are in the queue
