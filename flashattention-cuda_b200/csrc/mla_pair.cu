@@ -185,24 +185,24 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // tiles ahead of the P V: tile j reuses the score buffer of tile j - 2, free once P of j - 2 is out.
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, true, false, false);
       bool ok = mbar_wait(bar(Q_FULL), 0, s_abort, p.status, P2_ERR_Q) && mbar_wait(bar(QT_READY), 0, s_abort, p.status, P2_ERR_QT);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ), 16);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int bf = j & 1;
         if (j >= 2) ok = mbar_wait(bar(P_READY + bf), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_P_READY);
         if (ok) ok = mbar_wait(bar(X_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), d_s = tm_s + 64 * bf;
+        const uint32_t t_lo = desc_lo(smem_u32(sT + bf * 9 * kPBlk), 16), d_s = tm_s + 64 * bf;
 #pragma unroll
         for (int k = 0; k < kPQT / 16; ++k)          // leading query dims from tensor memory
-          mma2_ts(d_s, tm_q + k * 8, smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, k > 0);
+          mma2_ts_w(d_s, tm_q + k * 8, t_lo + (((k >> 2) * kPBlk + (k & 3) * 32) >> 4), idesc_qk, k > 0);
         ok = mbar_wait(bar(X_FULLB + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // the other query dims from shared memory
           const int kq = k - kPQT / 16;
-          mma2_ss(d_s, smem_desc_sw128(smem_u32(sQ) + (kq >> 2) * kPBlk + (kq & 3) * 32, 16, 1024),
-                  smem_desc_sw128(t_base + (k >> 2) * kPBlk + (k & 3) * 32, 16, 1024), idesc_qk, 1u);
+          mma2_ss_w(d_s, q_lo + (((kq >> 2) * kPBlk + (kq & 3) * 32) >> 4), t_lo + (((k >> 2) * kPBlk + (k & 3) * 32) >> 4), idesc_qk, 1u);
         }
         mma2_commit_both(bar(S_FULL + bf));
       }
@@ -225,15 +225,14 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ok = mbar_wait(bar(P_READY + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_P_READY);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t_base = smem_u32(sT + bf * 9 * kPBlk), p_base = smem_u32(sP + bf * 2 * kPBlk);
+        const uint32_t v_lo = desc_lo(smem_u32(sT + bf * 9 * kPBlk), kPBlk), p_lo = desc_lo(smem_u32(sP + bf * 2 * kPBlk), 16);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const int h = ks >> 2;
-            mma2_ss(tm_o + 128 * s, smem_desc_sw128(p_base + h * kPBlk + (ks & 3) * 32, 16, 1024),
-                    smem_desc_sw128(t_base + (4 * s + 2 * h) * kPBlk + (ks & 3) * 2048, kPBlk, 1024), idesc_pv,
-                    (j > 0 || ks > 0) ? 1u : 0u);
+            mma2_ss_w(tm_o + 128 * s, p_lo + ((h * kPBlk + (ks & 3) * 32) >> 4),
+                      v_lo + (((4 * s + 2 * h) * kPBlk + (ks & 3) * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           }
           mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
         }

@@ -84,6 +84,24 @@ __device__ __forceinline__ void mma2_ts(uint32_t d, uint32_t a_tmem, uint64_t b,
                " tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
+// The same MMAs with the two 32-bit words of each shared-memory descriptor given separately: an issuing thread keeps
+// one low word per operand buffer (address >> 4 in bits 0-13, leading byte offset >> 4 in bits 16-29) and adds a
+// constant per k step; every descriptor here shares the high word (stride 1024 >> 4, descriptor version, 128-byte
+// swizzle).  Assembling 64-bit descriptors per MMA made the issuing thread, not the tensor pipe, set the pace.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3ffffu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__device__ __forceinline__ void mma2_ss_w(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+               " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n}\n"
+               ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void mma2_ts_w(uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n .reg .b64 db;\n setp.ne.b32 p, %5, 0;\n mov.b64 db, {%2, %3};\n"
+               " tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %4, p;\n}\n"
+               ::"r"(d), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(acc) : "memory");
+}
 // arrive on the barrier at this offset in both CTAs once every MMA issued so far has completed
 __device__ __forceinline__ void mma2_commit_both(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"

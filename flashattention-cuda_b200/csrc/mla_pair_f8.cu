@@ -59,15 +59,17 @@ constexpr int kFThreads = 384;                // 4 producer / issuer warps + 8 s
 constexpr int kFSoft = 256;                   // softmax threads
 constexpr int kFTiles = 3;                    // tile buffers (score and P buffers: two)
 
-__device__ __forceinline__ void mma2_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+// kind::f8f6f4 MMAs over the pair, descriptors as words (see mla_pair.cuh: one low word per operand buffer, a
+// constant added per step)
+__device__ __forceinline__ void mma2_f8_w(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n setp.ne.b32 p, %5, 0;\n mov.b64 da, {%1, %3};\n mov.b64 db, {%2, %3};\n"
+               " tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p;\n}\n"
+               ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(acc) : "memory");
 }
-__device__ __forceinline__ void mma2_f8_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
-  asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-               " tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], [%1], %2, %3, p;\n}\n"
-               ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+__device__ __forceinline__ void mma2_f8_ts_w(uint32_t d, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n .reg .pred p;\n .reg .b64 db;\n setp.ne.b32 p, %5, 0;\n mov.b64 db, {%2, %3};\n"
+               " tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], [%1], db, %4, p;\n}\n"
+               ::"r"(d), "r"(a_tmem), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(acc) : "memory");
 }
 __device__ __forceinline__ void softmax_bar256() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
 // two floats -> two E4M3 bytes (lo in bits 0..7), round to nearest, saturating
@@ -292,18 +294,19 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, false, false, false);    // format 0 of kind::f8f6f4 = E4M3
       bool ok = mbar_wait(bar(QT_READY), 0, s_abort, p.status, P2_ERR_QT);
       auto step_off = [](int t) { return t < 16 ? (t >> 2) * kPBlk + (t & 3) * 32 : 4 * kPBlk + 64 + (t - 16) * 32; };
+      const uint32_t q_lo = desc_lo(smem_u32(sQ), 16);
+      const uint32_t qr_lo = desc_lo(smem_u32(sQr), 16) - ((4 * kPBlk) >> 4);   // so that step_off(16), step_off(17) land in sQr
       for (int j = 0; ok && j < n_tiles; ++j) {
         const int sb = j & 1, tb = j % kFTiles, use = j / kFTiles;   // score buffer; tile buffer and its use count
         if (j >= 2) ok = mbar_wait(bar(P_READY + sb), ((j >> 1) - 1) & 1, s_abort, p.status, P2_ERR_P_READY);
         if (ok) ok = mbar_wait(bar(X_FULL + tb), use & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t_base = smem_u32(sT + tb * kFBlocks * kPBlk), q_base = smem_u32(sQ), d_s = tm_s + 64 * sb;
-        const uint32_t qr_base = smem_u32(sQr) - 4 * kPBlk;          // so that step_off(16), step_off(17) land in sQr
+        const uint32_t t_lo = desc_lo(smem_u32(sT + tb * kFBlocks * kPBlk), 16), d_s = tm_s + 64 * sb;
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
-          mma2_f8_ts(d_s, tm_q + 8 * t, smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, t > 0 ? 1u : 0u);
-          mma2_f8(d_s, smem_desc_sw128(q_base + step_off(t), 16, 1024), smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, 1u);
+          mma2_f8_ts_w(d_s, tm_q + 8 * t, t_lo + (step_off(t) >> 4), idesc_qk, t > 0 ? 1u : 0u);
+          mma2_f8_w(d_s, q_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
         }
         ok = mbar_wait(bar(X_FULLB + tb), use & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
@@ -311,10 +314,10 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
 #pragma unroll
         for (int t = 8; t < 18; ++t) {
           if (t < 16)
-            mma2_f8_ts(d_s, tm_q + 8 * t, smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, 1u);
+            mma2_f8_ts_w(d_s, tm_q + 8 * t, t_lo + (step_off(t) >> 4), idesc_qk, 1u);
           else
-            mma2_f8(d_s, smem_desc_sw128(qr_base + step_off(t), 16, 1024), smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, 1u);
-          mma2_f8(d_s, smem_desc_sw128(q_base + step_off(t), 16, 1024), smem_desc_sw128(t_base + step_off(t), 16, 1024), idesc_qk, 1u);
+            mma2_f8_w(d_s, qr_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
+          mma2_f8_w(d_s, q_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
         }
         mma2_commit_both(bar(S_FULL + sb));
       }
@@ -339,7 +342,7 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
         ok = mbar_wait(bar(P_READY + sb), (j >> 1) & 1, s_abort, p.status, P2_ERR_P_READY);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t_base = smem_u32(sT + tb * kFBlocks * kPBlk), p_base = smem_u32(sP + sb * 2 * kPBlk);
+        const uint32_t v_lo = desc_lo(smem_u32(sT + tb * kFBlocks * kPBlk), kPBlk), p_lo = desc_lo(smem_u32(sP + sb * 2 * kPBlk), 16);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
 #pragma unroll
@@ -347,9 +350,8 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
             const int h = hk >> 1, kk = hk & 1;
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc)
-              mma2_f8(tm_o + 128 * s, smem_desc_sw128(p_base + pc * kPBlk + hk * 32, 16, 1024),
-                      smem_desc_sw128(t_base + (2 * s + h) * kPBlk + kk * 4096, kPBlk, 1024), idesc_pv,
-                      (j > 0 || hk > 0 || pc > 0) ? 1u : 0u);
+              mma2_f8_w(tm_o + 128 * s, p_lo + ((pc * kPBlk + hk * 32) >> 4), v_lo + (((2 * s + h) * kPBlk + kk * 4096) >> 4), idesc_pv,
+                        (j > 0 || hk > 0 || pc > 0) ? 1u : 0u);
           }
           mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + tb));
         }
