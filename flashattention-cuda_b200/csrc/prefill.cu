@@ -244,11 +244,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, BF16, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(128, D, BF16, false, true);
-      // a wait whose barrier is usually complete already costs one instruction here; the bounded wait with its
-      // abort-flag and clock reads is entered only when the first try fails
-      auto wait = [&](int b, int parity, int code) {
-        return mbar_try_wait(bar(b), parity) || mbar_wait(bar(b), parity, s_abort, p.status, code);
-      };
+      auto wait = [&](int b, int parity, int code) { return mbar_wait(bar(b), parity, s_abort, p.status, code); };
       // low descriptor words of the operand buffers (address >> 4 in bits 0-13, leading byte offset >> 4 in bits
       // 16-29) and the high word all of them share (stride 1024 >> 4, descriptor version, 128-byte swizzle)
       const uint32_t hi_w = (1024u >> 4) | (1u << 14) | (2u << 29);

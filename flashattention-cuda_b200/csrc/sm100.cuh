@@ -37,8 +37,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  `abort_flag` is a CTA-shared int; `status` a global error word (may be null).
 __device__ __forceinline__ bool mbar_wait_cycles(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
                                                  long long max_cycles) {
-  if (*abort_flag) return false;
+  // a barrier that is complete already costs one instruction; the abort flag matters only to a thread that
+  // would otherwise sit here (a CTA whose wait gave up elsewhere drains through its completed barriers and
+  // stops at the first incomplete one)
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
