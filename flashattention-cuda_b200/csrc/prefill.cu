@@ -240,7 +240,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
+      // The whole warp walks the issuer's control flow (waits, counters, descriptor words), so that this arithmetic is
+      // warp-uniform; one elected lane executes the tcgen05 instructions.
+      const bool lead = elect_one();
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, BF16, false, false);
       constexpr uint32_t idesc_pv = idesc_f16(128, D, BF16, false, true);
@@ -258,20 +261,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       auto issue_qk = [&](int i, int gt) {              // gt: ring position of the key tile
         const uint32_t a0 = q_lo[i], b0 = k_lo[gt % STAGES], d = tmem + i * 128;
-        mma_ss_words<false>(d, a0, b0, hi_w, idesc_qk);
+        if (lead) {
+          mma_ss_words<false>(d, a0, b0, hi_w, idesc_qk);
 #pragma unroll
-        for (int k = 1; k < D / 16; ++k) {
-          const uint32_t off = ((k >> 2) * BLK_BYTES + (k & 3) * 32) >> 4;
-          mma_ss_words<true>(d, a0 + off, b0 + off, hi_w, idesc_qk);
+          for (int k = 1; k < D / 16; ++k) {
+            const uint32_t off = ((k >> 2) * BLK_BYTES + (k & 3) * 32) >> 4;
+            mma_ss_words<true>(d, a0 + off, b0 + off, hi_w, idesc_qk);
+          }
+          mma_commit(bar(S_FULL + i));
         }
-        mma_commit(bar(S_FULL + i));
       };
       auto issue_pv = [&](int i, int gt, bool first) {
         // A = P_i in tensor memory: 16 keys = 8 packed columns; B = V [128 keys][D], MN-major
         const uint32_t b0 = v_lo[gt % STAGES], d = tmem + 256 + i * 128, a = tmem + i * 128;
-        mma_ts_words(d, a, b0, hi_w, idesc_pv, first ? 0u : 1u);
+        if (lead) {
+          mma_ts_words(d, a, b0, hi_w, idesc_pv, first ? 0u : 1u);
 #pragma unroll
-        for (int k = 1; k < 8; ++k) mma_ts_words(d, a + k * 8, b0 + (k * 2048 >> 4), hi_w, idesc_pv, 1u);
+          for (int k = 1; k < 8; ++k) mma_ts_words(d, a + k * 8, b0 + (k * 2048 >> 4), hi_w, idesc_pv, 1u);
+        }
       };
       ItemWalk walk;
       int bh, qt, n_t[2];
@@ -290,7 +297,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // threads arrive there only after they have read the previous item's O_i.
         if (n_t[0] > 0) issue_qk(0, g);
         if (n_t[1] > 0) issue_qk(1, g);
-        if (n_max == 1) mma_commit(bar(Q_EMPTY));
+        if (lead && n_max == 1) mma_commit(bar(Q_EMPTY));
         for (int j = 0; ok && j < n_max; ++j) {
           const int gt = g + j;
 #pragma unroll
@@ -301,9 +308,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               ++n_p[i];
               tc_fence_after();
               issue_pv(i, gt, j == 0);
-              if (j + 1 == n_t[i]) mma_commit(bar(O_DONE + i));
+              if (lead && j + 1 == n_t[i]) mma_commit(bar(O_DONE + i));
             }
-            if (i == 1) mma_commit(bar(KV_EMPTY + (gt % STAGES)));
+            if (lead && i == 1) mma_commit(bar(KV_EMPTY + (gt % STAGES)));
             if (i == 0 && j + 1 < n_max) {   // the next key tile is only needed from here on
               ok = wait(KV_FULL + ((gt + 1) % STAGES), ((gt + 1) / STAGES) & 1, P2_ERR_KV_FULL);
               if (!ok) break;
@@ -311,7 +318,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             if (j + 1 < n_t[i]) issue_qk(i, gt + 1);
           }
-          if (ok && j + 2 == n_max) mma_commit(bar(Q_EMPTY));   // the item's last score MMAs are in the queue
+          if (lead && ok && j + 2 == n_max) mma_commit(bar(Q_EMPTY));   // the item's last score MMAs are in the queue
         }
         g += n_max;
       }
