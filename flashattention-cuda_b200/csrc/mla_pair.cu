@@ -178,7 +178,9 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0 && n_tiles > 0) {
+    if (rank == 0 && n_tiles > 0) {
+      // the whole warp walks the control flow (uniform arithmetic); one elected lane executes the tcgen05 instructions
+      const bool lead = elect_one();
       // ------------------------------------------------- score MMA issuer (even CTA, for the pair)
       // Two issuing threads (this one and warp 7) keep the tensor pipe fed across batch boundaries: while
       // one is blocked behind its own batch the other has the next one queued.  Scores run at most two
@@ -193,22 +195,28 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         const uint32_t t_lo = desc_lo(smem_u32(sT + bf * 9 * kPBlk), 16), d_s = tm_s + 64 * bf;
+        if (lead) {
 #pragma unroll
-        for (int k = 0; k < kPQT / 16; ++k)          // leading query dims from tensor memory
-          mma2_ts_w(d_s, tm_q + k * 8, t_lo + (((k >> 2) * kPBlk + (k & 3) * 32) >> 4), idesc_qk, k > 0);
+          for (int k = 0; k < kPQT / 16; ++k)          // leading query dims from tensor memory
+            mma2_ts_w(d_s, tm_q + k * 8, t_lo + (((k >> 2) * kPBlk + (k & 3) * 32) >> 4), idesc_qk, k > 0);
+        }
         ok = mbar_wait(bar(X_FULLB + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
         tc_fence_after();
+        if (lead) {
 #pragma unroll
-        for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // the other query dims from shared memory
-          const int kq = k - kPQT / 16;
-          mma2_ss_w(d_s, q_lo + (((kq >> 2) * kPBlk + (kq & 3) * 32) >> 4), t_lo + (((k >> 2) * kPBlk + (k & 3) * 32) >> 4), idesc_qk, 1u);
+          for (int k = kPQT / 16; k < kPDQK / 16; ++k) {   // the other query dims from shared memory
+            const int kq = k - kPQT / 16;
+            mma2_ss_w(d_s, q_lo + (((kq >> 2) * kPBlk + (kq & 3) * 32) >> 4), t_lo + (((k >> 2) * kPBlk + (k & 3) * 32) >> 4), idesc_qk, 1u);
+          }
+          mma2_commit_both(bar(S_FULL + bf));
         }
-        mma2_commit_both(bar(S_FULL + bf));
       }
     }
   } else if (warp == 7) {
-    if (lane == 0 && rank == 0 && n_tiles > 0) {
+    if (rank == 0 && n_tiles > 0) {
+      // the whole warp walks the control flow (uniform arithmetic); one elected lane executes the tcgen05 instructions
+      const bool lead = elect_one();
       // ------------------------------------------------- P V MMA issuer (even CTA, for the pair)
       constexpr uint32_t idesc_pv = idesc_f16(128, 256, true, false, true);
       bool ok = true;
@@ -216,7 +224,7 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int bf = j & 1;
         ok = mbar_wait(bar(R_FULL + bf), (j >> 1) & 1, s_abort, p.status, P2_ERR_Y_FULL);
         if (!ok) break;
-        if (ragged_end && j + 1 == n_tiles) {
+        if (lead && ragged_end && j + 1 == n_tiles) {
           // everything of the last tile has landed in both CTAs: let the softmax threads clear the value
           // rows past the end of the sequence
           mbar_arrive(bar(Z_GO));
@@ -228,13 +236,15 @@ mla_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint32_t v_lo = desc_lo(smem_u32(sT + bf * 9 * kPBlk), kPBlk), p_lo = desc_lo(smem_u32(sP + bf * 2 * kPBlk), 16);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
+          if (lead) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const int h = ks >> 2;
-            mma2_ss_w(tm_o + 128 * s, p_lo + ((h * kPBlk + (ks & 3) * 32) >> 4),
-                      v_lo + (((4 * s + 2 * h) * kPBlk + (ks & 3) * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < 8; ++ks) {
+              const int h = ks >> 2;
+              mma2_ss_w(tm_o + 128 * s, p_lo + ((h * kPBlk + (ks & 3) * 32) >> 4),
+                        v_lo + (((4 * s + 2 * h) * kPBlk + (ks & 3) * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+            }
+            mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
           }
-          mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + bf));
         }
       }
     }

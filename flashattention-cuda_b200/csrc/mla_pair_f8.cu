@@ -285,7 +285,9 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0 && n_tiles > 0) {
+    if (rank == 0 && n_tiles > 0) {
+      // the whole warp walks the control flow (uniform arithmetic); one elected lane executes the tcgen05 instructions
+      const bool lead = elect_one();
       // ------------------------------------------------- score MMA issuer (even CTA, for the pair)
       // Two issuing threads (this one and warp 3) keep the tensor pipe fed across batch boundaries.  Scores
       // run at most two tiles ahead of the P V: tile j reuses the score buffer of tile j - 2, free once P of
@@ -303,27 +305,33 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
         if (!ok) break;
         tc_fence_after();
         const uint32_t t_lo = desc_lo(smem_u32(sT + tb * kFBlocks * kPBlk), 16), d_s = tm_s + 64 * sb;
+        if (lead) {
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          mma2_f8_ts_w(d_s, tm_q + 8 * t, t_lo + (step_off(t) >> 4), idesc_qk, t > 0 ? 1u : 0u);
-          mma2_f8_w(d_s, q_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
+          for (int t = 0; t < 8; ++t) {
+            mma2_f8_ts_w(d_s, tm_q + 8 * t, t_lo + (step_off(t) >> 4), idesc_qk, t > 0 ? 1u : 0u);
+            mma2_f8_w(d_s, q_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
+          }
         }
         ok = mbar_wait(bar(X_FULLB + tb), use & 1, s_abort, p.status, P2_ERR_X_FULL);
         if (!ok) break;
         tc_fence_after();
+        if (lead) {
 #pragma unroll
-        for (int t = 8; t < 18; ++t) {
-          if (t < 16)
-            mma2_f8_ts_w(d_s, tm_q + 8 * t, t_lo + (step_off(t) >> 4), idesc_qk, 1u);
-          else
-            mma2_f8_w(d_s, qr_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
-          mma2_f8_w(d_s, q_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
+          for (int t = 8; t < 18; ++t) {
+            if (t < 16)
+              mma2_f8_ts_w(d_s, tm_q + 8 * t, t_lo + (step_off(t) >> 4), idesc_qk, 1u);
+            else
+              mma2_f8_w(d_s, qr_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
+            mma2_f8_w(d_s, q_lo + (step_off(t) >> 4), t_lo + (step_off(t) >> 4), idesc_qk, 1u);
+          }
+          mma2_commit_both(bar(S_FULL + sb));
         }
-        mma2_commit_both(bar(S_FULL + sb));
       }
     }
   } else if (warp == 3) {
-    if (lane == 0 && rank == 0 && n_tiles > 0) {
+    if (rank == 0 && n_tiles > 0) {
+      // the whole warp walks the control flow (uniform arithmetic); one elected lane executes the tcgen05 instructions
+      const bool lead = elect_one();
       // ------------------------------------------------- P V MMA issuer (even CTA, for the pair)
       // Per value segment s: key half h, 32-key step kk, piece pc.  A = P piece (row-major over the 128 keys of
       // the tile), B = value block 2 s + h (keys down, 128 columns across: the transposed, MN-major form).
@@ -333,7 +341,7 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
         const int sb = j & 1, tb = j % kFTiles, use = j / kFTiles;
         ok = mbar_wait(bar(R_FULL + tb), use & 1, s_abort, p.status, P2_ERR_Y_FULL);
         if (!ok) break;
-        if (ragged_end && j + 1 == n_tiles) {
+        if (lead && ragged_end && j + 1 == n_tiles) {
           // everything of the last tile has landed in both CTAs: let the softmax threads clear the value
           // rows past the end of the sequence
           mbar_arrive(bar(Z_GO));
@@ -345,15 +353,17 @@ mla_pair_f8_kernel(const __grid_constant__ CUtensorMap map_l, const MlaPairParam
         const uint32_t v_lo = desc_lo(smem_u32(sT + tb * kFBlocks * kPBlk), kPBlk), p_lo = desc_lo(smem_u32(sP + sb * 2 * kPBlk), 16);
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
+          if (lead) {
 #pragma unroll
-          for (int hk = 0; hk < 4; ++hk) {
-            const int h = hk >> 1, kk = hk & 1;
+            for (int hk = 0; hk < 4; ++hk) {
+              const int h = hk >> 1, kk = hk & 1;
 #pragma unroll
-            for (int pc = 0; pc < 2; ++pc)
-              mma2_f8_w(tm_o + 128 * s, p_lo + ((pc * kPBlk + hk * 32) >> 4), v_lo + (((2 * s + h) * kPBlk + kk * 4096) >> 4), idesc_pv,
-                        (j > 0 || hk > 0 || pc > 0) ? 1u : 0u);
+              for (int pc = 0; pc < 2; ++pc)
+                mma2_f8_w(tm_o + 128 * s, p_lo + ((pc * kPBlk + hk * 32) >> 4), v_lo + (((2 * s + h) * kPBlk + kk * 4096) >> 4), idesc_pv,
+                          (j > 0 || hk > 0 || pc > 0) ? 1u : 0u);
+            }
+            mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + tb));
           }
-          mma2_commit_both(bar((s == 0 ? T_FREEA : T_FREE) + tb));
         }
       }
     }
