@@ -239,8 +239,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
+    if (n_tiles > 0) {
       // ------------------------------------------------- MMA issuer
+      // the whole warp walks the control flow (uniform arithmetic); one elected lane executes the tcgen05 instructions
+      const bool lead = elect_one();
       // The scores of tile j are issued before the weights of tile j - 2 (the previous tile of the same stream)
       // are waited for, so that the tensor core works on S^T(j) while both warpgroups are busy.
       constexpr uint32_t idesc_qk = idesc_f16(128, 16, false, false, false);   // format 0 of kind::f8f6f4 = E4M3
@@ -254,11 +256,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
           if (!ok) break;
           tc_fence_after();
           const uint32_t k_base = smem_u32(sK + st * kTBlk), q_base = smem_u32(sQ);
+          if (lead) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_f8_ss(tm_s + 16 * sb, smem_desc_sw128(k_base + ks * 32, 16, 1024), smem_desc_sw128(q_base + ks * 32, 16, 1024),
-                      idesc_qk, ks > 0 ? 1u : 0u);
-          mma_commit(bar(S_FULL + sb));
+            for (int ks = 0; ks < 4; ++ks)
+              mma_f8_ss(tm_s + 16 * sb, smem_desc_sw128(k_base + ks * 32, 16, 1024), smem_desc_sw128(q_base + ks * 32, 16, 1024),
+                        idesc_qk, ks > 0 ? 1u : 0u);
+            mma_commit(bar(S_FULL + sb));
+          }
         }
         if (j >= 2) {
           const int jj = j - 2, st = jj % kTStages, sb = jj & 3;
@@ -266,12 +270,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
           if (!ok) break;
           tc_fence_after();
           const uint32_t v_base = smem_u32(sV + st * kTBlk), p_base = smem_u32(sP + sb * kTSmall);
+          if (lead) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_f8_ss(tm_o + 16 * (jj & 1), smem_desc_sw128(v_base + ks * 4096, kTBlk, 1024), smem_desc_sw128(p_base + ks * 32, 16, 1024),
-                      idesc_pv, (jj >= 2 || ks > 0) ? 1u : 0u);
-          mma_commit(bar(EMPTY + st));
-          mma_commit(bar(PV_DONE + sb));
+            for (int ks = 0; ks < 4; ++ks)
+              mma_f8_ss(tm_o + 16 * (jj & 1), smem_desc_sw128(v_base + ks * 4096, kTBlk, 1024), smem_desc_sw128(p_base + ks * 32, 16, 1024),
+                        idesc_pv, (jj >= 2 || ks > 0) ? 1u : 0u);
+            mma_commit(bar(EMPTY + st));
+            mma_commit(bar(PV_DONE + sb));
+          }
         }
       }
     }
