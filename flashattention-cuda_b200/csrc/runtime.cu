@@ -52,6 +52,12 @@ extern "C" const char* fa_status_text(int status_word) {
     case 47: wait = "MLA pair kernel: wait for the scores timed out"; break;
     case 48: wait = "MLA pair kernel: wait for P timed out"; break;
     case 49: wait = "MLA pair kernel: wait for a P V batch timed out"; break;
+    case 52: wait = "MLA pair kernel: wait for the token scales timed out"; break;
+    case 61: case 62: wait = "FP8 tcgen05 decode: wait on a K/V stage timed out"; break;
+    case 63: case 64: wait = "FP8 tcgen05 decode: wait on a score buffer timed out"; break;
+    case 65: wait = "FP8 tcgen05 decode: wait for P timed out"; break;
+    case 66: wait = "FP8 tcgen05 decode: wait for a P V batch timed out"; break;
+    case 67: wait = "FP8 tcgen05 decode: wait for the query operand timed out"; break;
     default: wait = "a bounded device wait timed out"; break;
   }
   snprintf(buf, sizeof buf, "%s%s%s (status 0x%x)", wait, (code && (status_word & FA_STATUS_BAD_BLOCK_TABLE)) ? "; " : "",

@@ -56,7 +56,7 @@ FA_API int fa_version(void);
  *   bit 16 (FA_STATUS_BAD_BLOCK_TABLE): a block-table entry outside [0, num_blocks) was met; the page was
  *           treated as masked (decode) or read from block 0 (MLA tensor-core kernel), the output is wrong
  *   bits 0..15: code of the first pipeline wait that gave up after its cycle bound (21..27 dense attention,
- *           41..49 MLA CTA-pair kernel); the kernel ended early and the output is invalid
+ *           41..52 MLA CTA-pair kernels, 61..67 FP8 tcgen05 decode); the kernel ended early and the output is invalid
  * A non-zero word after a launch also means the arrival counters behind it may not be zero again: zero
  * the whole counters buffer before the next launch.  (The reference has no counterpart: its kernels read
  * whatever the table holds, kernels/v8_gqa_ss/gqa_ss_attention.cu:124-136.) */
