@@ -22,13 +22,18 @@
 // P <= 256 in half precision and makes TMEM round trips of O rare.
 // The output leaves through shared memory and TMA stores (32 rows x 128 bytes per warp and pass).
 //
-// Measured on B = 4, H = 32, N = 4096, d = 128 fp16 (CUDA events, same GPU): one CTA per item with row-by-row
-// output stores 0.651 ms; this kernel 0.589 ms.  A clock64 trace of the item boundary showed why: the
-// row-by-row stores (each warp instruction touching 32 lines) kept the SM's memory path busy for ~4000 cycles per
-// warpgroup, the next item's Q load finished only after them (8000-9000 cycles after it was issued) and the
-// first score MMAs ran at a tenth of their speed meanwhile.  A score or value MMA (M = 128, N = 128, K = 16)
-// takes ~97 cycles here, so the 16 MMAs of a tile step keep the tensor pipe busy for ~1500 of the ~2200 cycles a
-// step takes in steady state.
+// Measured on B = 4, H = 32, N = 4096, d = 128 fp16 (CUDA events, A/B on one GPU each):
+//   one CTA per item, row-by-row output stores, 64-bit descriptors assembled per MMA by a single issuing lane  0.651 ms
+//   persistent CTAs + TMA-store epilogue                                                                       0.589 ms
+//   MMAs issued from precomputed 32-bit descriptor words (0.587 ->)                                            0.547 ms
+//   barrier waits that try the barrier before reading the abort flag (0.545 ->)                                0.535 ms
+//   issuing warp walks the control flow whole, one elected lane executes the tcgen05 instructions (0.512 ->)  0.482 ms
+// (0.50-0.51 ms = 65-66 % of the measured dense bf16 peak in the benchmark runs).  A clock64 trace of the item boundary
+// showed why the stores mattered: row-by-row stores (each warp instruction touching 32 lines) kept the SM's memory path
+// busy for ~4000 cycles per warpgroup, the next item's Q load finished only after them (8000-9000 cycles after it was
+// issued) and the first score MMAs ran at a tenth of their speed meanwhile.  The other three steps all shorten the
+// issuing thread's own instruction stream, which sets the pace between MMA batches: in isolation an M = 128, N = 128,
+// K = 16 MMA takes 64 cycles; with descriptors assembled per MMA by one lane of a diverged warp the kernel saw 80-98.
 // Measured and not kept: two exponentials per instruction (ex2.approx.f16x2) +0.6 %; two threads per query row
 // (four softmax warpgroups) +7 %; two 64-key score buffers per query tile +30 %; the exponentials of a tile taken
 // against the reference maximum as it stands while the tile's own maximum is found alongside (so that no pass
